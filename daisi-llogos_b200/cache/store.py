@@ -1,9 +1,9 @@
 """The cache of live sequences: paged keys/values per storage group, and fixed-size state.
 
 Layers are put into groups by what they need.  A key/value group is defined by
-(key/value heads, head size, window): all its layers share one page table per sequence and
+(key/value heads, head size, window, value head size): all its layers share one page table per sequence and
 one pool of pages, and each layer has its own key and value pages
-``[n_pages, n_kv, 64, head_dim]``.  A group with a window keeps a ring of
+``[n_pages, n_kv, 64, head_dim]`` (the value pages with the value heads' size where that differs).  A group with a window keeps a ring of
 ``ceil(window / 64) + 1`` pages per sequence; a group without keeps every page.  Besides,
 every layer that declares a fixed-size state gets ``[n_slots, *shape]``, zeroed when a
 sequence starts (the reference keeps such state for its recurrent layers, one sequence only:
@@ -73,8 +73,9 @@ class KvGroup:
         self.page_table = torch.zeros((n_slots + 1, self.table_width), dtype=torch.int32, device=device)
         self.page_table[n_slots, :] = n_pages
         shape = (n_pages + 1, need.num_kv_heads, PAGE, need.head_dim)
+        v_shape = (n_pages + 1, need.num_kv_heads, PAGE, need.value_dim or need.head_dim)
         self.k = {u: torch.zeros(shape, dtype=dtype, device=device) for u in units}
-        self.v = {u: torch.zeros(shape, dtype=dtype, device=device) for u in units}
+        self.v = {u: torch.zeros(v_shape, dtype=dtype, device=device) for u in units}
 
     def pages_needed(self, length: int) -> int:
         return min(pages_for(length), self.ring_pages)

@@ -35,11 +35,20 @@ def known_architectures():
     return sorted(_ARCHITECTURES)
 
 
-def architecture_of(config_dict: Mapping[str, Any]) -> Architecture:
+def architecture_name(config_dict: Mapping[str, Any]) -> str:
+    """The name a config.json files its model under: the first entry of ``architectures`` (a list), or, in
+    files that carry no such list, the string under ``architecture``."""
     archs = config_dict.get("architectures")
-    if not isinstance(archs, (list, tuple)) or not archs:
-        raise ConfigError("config.json: missing key 'architectures' (a non-empty list of names)")
-    name = archs[0]
+    if isinstance(archs, (list, tuple)) and archs and isinstance(archs[0], str):
+        return archs[0]
+    one = config_dict.get("architecture")
+    if archs is None and isinstance(one, str) and one:
+        return one
+    raise ConfigError("config.json: missing key 'architectures' (a non-empty list of names) or 'architecture' (a name)")
+
+
+def architecture_of(config_dict: Mapping[str, Any]) -> Architecture:
+    name = architecture_name(config_dict)
     if name not in _ARCHITECTURES:
         raise ConfigError(
             f"config.json: architecture '{name}' is not registered (known: {', '.join(known_architectures())})")
@@ -122,3 +131,7 @@ def _dense_reader(*, qk_norm: bool, force_bias: bool):
 register_architecture("LlamaForCausalLM", _dense_reader(qk_norm=False, force_bias=False), dense_decoder_spec)
 register_architecture("Qwen2ForCausalLM", _dense_reader(qk_norm=False, force_bias=True), dense_decoder_spec)
 register_architecture("Qwen3ForCausalLM", _dense_reader(qk_norm=True, force_bias=False), dense_decoder_spec)
+
+from . import karitar as _karitar  # noqa: E402  (its module needs the part specs imported above)
+
+register_architecture(_karitar.NAME, _karitar.KaritarConfig.from_dict, _karitar.karitar_spec)

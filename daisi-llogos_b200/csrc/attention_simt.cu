@@ -12,6 +12,10 @@
 // (Daisi.Llogos.Cpu/CpuBackend.cs:476-590; Daisi.Llogos.Cuda/kernels/composite_ops.cu:275-387
 // for one token, :396-512 for several): score = (q . k) * scale with scale applied after the
 // dot product, running maximum, exponentials, sum, weighted values, division by the sum.
+//
+// Further forms, all by argument (kernel_args.h): value heads of another size than the key heads (vd), a sink (a score
+// that joins the softmax's denominator and carries no value: p_j = e^{s_j} / (e^{sink} + sum e^{s_j})), and a gate per
+// (token, head) that multiplies the head's output.
 #include "common.cuh"
 #include "kernel_args.h"
 
@@ -28,11 +32,11 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
   extern __shared__ float sm[];
   __shared__ long long src_off[KT];
   __shared__ int src_new[KT];
-  const int hd = a.hd;
+  const int hd = a.hd, vd = a.vd > 0 ? a.vd : a.hd;
   float* Qs = sm;                          // [BQ][hd]
   float* Ks = Qs + BQ * hd;                // [KT][hd + 1]
-  float* Vs = Ks + KT * (hd + 1);          // [KT][hd]
-  float* Ps = Vs + KT * hd;                // [BQ][KT]
+  float* Vs = Ks + KT * (hd + 1);          // [KT][vd]
+  float* Ps = Vs + KT * vd;                // [BQ][KT]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int b = a.tiles[2 * blockIdx.x], q_off = a.tiles[2 * blockIdx.x + 1];
   const int h = blockIdx.y, kvh = h / (a.nh / a.nkv);
@@ -67,10 +71,10 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
       if (kp < k_end) {
         if (kp >= lb) {
           src_new[tid] = 1;
-          src_off[tid] = ((long long)(tok0 + kp - lb) * a.nkv + kvh) * hd;
+          src_off[tid] = (long long)(tok0 + kp - lb) * a.nkv + kvh;
         } else {
           src_new[tid] = 0;
-          src_off[tid] = kv_row(a.page_table, a.table_width, a.ring_pages, slot, kp, kvh, a.nkv) * hd;
+          src_off[tid] = kv_row(a.page_table, a.table_width, a.ring_pages, slot, kp, kvh, a.nkv);
         }
       } else {
         src_new[tid] = -1;
@@ -80,17 +84,19 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
     __syncthreads();
     for (int idx = tid; idx < KT * hd; idx += 128) {
       const int j = idx / hd, d = idx % hd;
-      float kv = 0.f, vv = 0.f;
+      float kv = 0.f;
       const int sn = src_new[j];
-      if (sn == 1) {
-        kv = to_f32(((const T*)a.k_new)[src_off[j] + d]);
-        vv = to_f32(((const T*)a.v_new)[src_off[j] + d]);
-      } else if (sn == 0) {
-        kv = to_f32(((const T*)a.k_pages)[src_off[j] + d]);
-        vv = to_f32(((const T*)a.v_pages)[src_off[j] + d]);
-      }
+      if (sn == 1) kv = to_f32(((const T*)a.k_new)[src_off[j] * hd + d]);
+      else if (sn == 0) kv = to_f32(((const T*)a.k_pages)[src_off[j] * hd + d]);
       Ks[j * (hd + 1) + d] = kv;
-      Vs[j * hd + d] = vv;
+    }
+    for (int idx = tid; idx < KT * vd; idx += 128) {
+      const int j = idx / vd, d = idx % vd;
+      float vv = 0.f;
+      const int sn = src_new[j];
+      if (sn == 1) vv = to_f32(((const T*)a.v_new)[src_off[j] * vd + d]);
+      else if (sn == 0) vv = to_f32(((const T*)a.v_pages)[src_off[j] * vd + d]);
+      Vs[j * vd + d] = vv;
     }
     __syncthreads();
     const int kp = kt + lane;
@@ -123,9 +129,9 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
 #pragma unroll
       for (int dd = 0; dd < MAXD; ++dd) {
         const int d = lane + 32 * dd;
-        if (d < hd) {
+        if (d < vd) {
           float o = acc[i][dd];
-          for (int j = 0; j < KT; ++j) o = fmaf(prow[j], Vs[j * hd + d], o);
+          for (int j = 0; j < KT; ++j) o = fmaf(prow[j], Vs[j * vd + d], o);
           acc[i][dd] = o;
         }
       }
@@ -136,11 +142,18 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
   for (int i = 0; i < 4; ++i) {
     const int qi = warp * 4 + i;
     if (qi >= nq) continue;
-    const float inv = l[i] > 0.f ? 1.0f / l[i] : 0.f;
+    float li = l[i], keep = 1.f;
+    if (a.has_sink) {                       // the sink joins the sum; the values' weights shrink with it
+      const float m_all = fmaxf(m[i], a.sink_score);
+      keep = expf(m[i] - m_all);
+      li = li * keep + expf(a.sink_score - m_all);
+    }
+    float inv = li > 0.f ? keep / li : 0.f;
+    if (a.gate) inv *= a.gate[(long long)(tok0 + q_off + qi) * a.nh + h];
 #pragma unroll
     for (int dd = 0; dd < MAXD; ++dd) {
       const int d = lane + 32 * dd;
-      if (d < hd) out[((long long)(tok0 + q_off + qi) * a.nh + h) * hd + d] = from_f32<T>(acc[i][dd] * inv);
+      if (d < vd) out[((long long)(tok0 + q_off + qi) * a.nh + h) * vd + d] = from_f32<T>(acc[i][dd] * inv);
     }
   }
 }
@@ -152,14 +165,14 @@ constexpr int GC = 8;  // query heads of one key/value head handled per pass
 template <typename T>
 __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
   extern __shared__ float sm[];
-  const int hd = a.hd;
+  const int hd = a.hd, vd = a.vd > 0 ? a.vd : a.hd;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int G = a.nh / a.nkv;
   float* Qs = sm;                                   // [GC][hd]
   float* Kt = Qs + GC * hd + warp * (KT * (hd + 1) + GC * KT);   // per warp: [KT][hd + 1]
   float* Pw = Kt + KT * (hd + 1);                   // per warp: [GC][KT]
-  float* merge = Qs + GC * hd;                      // reused after the key loop: [4][GC][hd + 2]
+  float* merge = Qs + GC * hd;                      // reused after the key loop: [4][GC][vd + 2]
 
   const int len = a.len_before[b] + 1;
   const int slot = a.slots[b];
@@ -226,8 +239,8 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
 #pragma unroll
         for (int dd = 0; dd < MAXD; ++dd) {
           const int d = lane + 32 * dd;
-          if (d < hd) {
-            const float v = to_f32(vp_base[rj * hd + d]);
+          if (d < vd) {
+            const float v = to_f32(vp_base[rj * vd + d]);
 #pragma unroll
             for (int g = 0; g < GC; ++g)
               if (g < ng) acc[g][dd] = fmaf(Pw[g * KT + j], v, acc[g][dd]);
@@ -240,15 +253,15 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
 #pragma unroll
     for (int g = 0; g < GC; ++g) {
       if (g >= ng) break;
-      float* dst = merge + ((warp * GC + g) * (hd + 2));
+      float* dst = merge + ((warp * GC + g) * (vd + 2));
 #pragma unroll
       for (int dd = 0; dd < MAXD; ++dd) {
         const int d = lane + 32 * dd;
-        if (d < hd) dst[d] = acc[g][dd];
+        if (d < vd) dst[d] = acc[g][dd];
       }
       if (lane == 0) {
-        dst[hd] = m[g];
-        dst[hd + 1] = l[g];
+        dst[vd] = m[g];
+        dst[vd + 1] = l[g];
       }
     }
     __syncthreads();
@@ -256,22 +269,22 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
       float mw[4], M = -INFINITY;
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
-        mw[w] = merge[(w * GC + g) * (hd + 2) + hd];
+        mw[w] = merge[(w * GC + g) * (vd + 2) + vd];
         M = fmaxf(M, mw[w]);
       }
       float L = 0.f, sc[4];
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
         sc[w] = (M == -INFINITY) ? 0.f : expf(mw[w] - M);
-        L += sc[w] * merge[(w * GC + g) * (hd + 2) + hd + 1];
+        L += sc[w] * merge[(w * GC + g) * (vd + 2) + vd + 1];
       }
       const int h = kvh * G + g0 + g;
       const long long pidx = ((long long)b * a.nh + h) * a.n_splits + split;
-      for (int d = lane; d < hd; d += 32) {
+      for (int d = lane; d < vd; d += 32) {
         float o = 0.f;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) o += sc[w] * merge[(w * GC + g) * (hd + 2) + d];
-        a.part_o[pidx * hd + d] = o;
+        for (int w = 0; w < 4; ++w) o += sc[w] * merge[(w * GC + g) * (vd + 2) + d];
+        a.part_o[pidx * vd + d] = o;
       }
       if (lane == 0) {
         a.part_ml[pidx * 2] = M;
@@ -283,17 +296,21 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
 
 template <typename T>
 __global__ void attn_decode_reduce_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                          T* __restrict__ out, int nh, int hd, int n_splits) {
+                                          T* __restrict__ out, int nh, int hd, int n_splits, int has_sink,
+                                          float sink_score, const float* __restrict__ gate) {
+  // (hd: elements of a value head)
   const int h = blockIdx.x, b = blockIdx.y;
   const long long base = ((long long)b * nh + h) * n_splits;
   float M = -INFINITY;
   for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-  float L = 0.f;
+  if (has_sink) M = fmaxf(M, sink_score);
+  float L = has_sink ? expf(sink_score - M) : 0.f;
   for (int s = 0; s < n_splits; ++s) {
     const float ms = part_ml[(base + s) * 2];
     if (ms != -INFINITY) L += expf(ms - M) * part_ml[(base + s) * 2 + 1];
   }
-  const float inv = L > 0.f ? 1.0f / L : 0.f;
+  float inv = L > 0.f ? 1.0f / L : 0.f;
+  if (gate) inv *= gate[(long long)b * nh + h];
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float o = 0.f;
     for (int s = 0; s < n_splits; ++s) {
@@ -311,10 +328,12 @@ LLG_API int llg_attn_prefill_simt(const PrefillArgs* args, int dtype, cudaStream
   LLG_REQUIRE(a.nh > 0 && a.nkv > 0 && a.nh % a.nkv == 0, "attn_prefill: %d heads are no multiple of %d key/value heads",
               a.nh, a.nkv);
   LLG_REQUIRE(a.hd > 0 && a.hd <= 32 * MAXD, "attn_prefill: head_dim %d is outside [1, %d]", a.hd, 32 * MAXD);
+  LLG_REQUIRE(a.vd >= 0 && a.vd <= 32 * MAXD, "attn_prefill: value head size %d is outside [1, %d]", a.vd, 32 * MAXD);
+  const int vd = a.vd > 0 ? a.vd : a.hd;
   LLG_REQUIRE(a.window >= 0 && a.ring_pages > 0 && a.table_width >= a.ring_pages, "attn_prefill: bad cache geometry");
   LLG_REQUIRE(a.nh <= 65535, "attn_prefill: too many heads");
   if (a.n_tiles <= 0) return 0;
-  const size_t smem = (size_t)(BQ * a.hd + KT * (a.hd + 1) + KT * a.hd + BQ * KT) * sizeof(float);
+  const size_t smem = (size_t)(BQ * a.hd + KT * (a.hd + 1) + KT * vd + BQ * KT) * sizeof(float);
   dim3 grid(a.n_tiles, a.nh);
   cudaError_t e;
   if (dtype == LLG_F32) {
@@ -341,13 +360,15 @@ LLG_API int llg_attn_decode_simt(const DecodeArgs* args, void* out, int dtype, c
   LLG_REQUIRE(a.nh > 0 && a.nkv > 0 && a.nh % a.nkv == 0, "attn_decode: %d heads are no multiple of %d key/value heads",
               a.nh, a.nkv);
   LLG_REQUIRE(a.hd > 0 && a.hd <= 32 * MAXD, "attn_decode: head_dim %d is outside [1, %d]", a.hd, 32 * MAXD);
+  LLG_REQUIRE(a.vd >= 0 && a.vd <= 32 * MAXD, "attn_decode: value head size %d is outside [1, %d]", a.vd, 32 * MAXD);
+  const int vd = a.vd > 0 ? a.vd : a.hd;
   LLG_REQUIRE(a.n_splits >= 1 && a.n_splits <= 65535, "attn_decode: n_splits %d", a.n_splits);
   LLG_REQUIRE(a.window >= 0 && a.ring_pages > 0 && a.table_width >= a.ring_pages, "attn_decode: bad cache geometry");
   LLG_REQUIRE(a.nkv <= 65535 && a.n_seqs <= 65535, "attn_decode: grid too large");
   if (a.n_seqs <= 0) return 0;
   const size_t per_warp = (size_t)KT * (a.hd + 1) + GC * KT;
   size_t floats = (size_t)GC * a.hd + 4 * per_warp;
-  const size_t merge_floats = (size_t)GC * a.hd + 4 * GC * (a.hd + 2);
+  const size_t merge_floats = (size_t)GC * a.hd + 4 * GC * (vd + 2);
   if (merge_floats > floats) floats = merge_floats;
   const size_t smem = floats * sizeof(float);
   dim3 grid(a.n_splits, a.nkv, a.n_seqs);
@@ -357,13 +378,14 @@ LLG_API int llg_attn_decode_simt(const DecodeArgs* args, void* out, int dtype, c
     e = cudaFuncSetAttribute(attn_decode_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return llg_fail("attn_decode: shared memory %zu: %s", smem, cudaGetErrorString(e));
     attn_decode_kernel<float><<<grid, 128, smem, stream>>>(a);
-    attn_decode_reduce_kernel<float><<<rgrid, 64, 0, stream>>>(a.part_o, a.part_ml, (float*)out, a.nh, a.hd, a.n_splits);
+    attn_decode_reduce_kernel<float><<<rgrid, 64, 0, stream>>>(a.part_o, a.part_ml, (float*)out, a.nh, vd, a.n_splits,
+                                                               a.has_sink, a.sink_score, a.gate);
   } else if (dtype == LLG_BF16) {
     e = cudaFuncSetAttribute(attn_decode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return llg_fail("attn_decode: shared memory %zu: %s", smem, cudaGetErrorString(e));
     attn_decode_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(a);
-    attn_decode_reduce_kernel<__nv_bfloat16><<<rgrid, 64, 0, stream>>>(a.part_o, a.part_ml, (__nv_bfloat16*)out, a.nh, a.hd,
-                                                                        a.n_splits);
+    attn_decode_reduce_kernel<__nv_bfloat16><<<rgrid, 64, 0, stream>>>(a.part_o, a.part_ml, (__nv_bfloat16*)out, a.nh, vd,
+                                                                        a.n_splits, a.has_sink, a.sink_score, a.gate);
   } else {
     return llg_fail("attn_decode: unknown dtype %d", dtype);
   }
@@ -422,5 +444,9 @@ int llg_attn_decode_noalloc(const void* q, const void* k_pages, const void* v_pa
   a.n_splits = n_splits;
   a.scale = scale;
   a.window = window;
+  a.vd = 0;
+  a.has_sink = 0;
+  a.sink_score = 0.f;
+  a.gate = nullptr;
   return llg_attn_decode_simt(&a, out, dtype, stream);
 }

@@ -708,3 +708,226 @@ LLG_API int llg_zero_rows(void* base, const int* rows, int n_rows, long long row
   zero_rows_kernel<<<n_rows, 256, 0, stream>>>((unsigned char*)base, rows, row_bytes);
   return llg_check_launch("zero_rows");
 }
+
+// ---- residual in several streams (hyper-connections) ----------------------------------
+
+// See HyperNormArgs in kernel_args.h.  One block per output row; the read-out u stays in shared memory between the
+// pass that updates the streams and the pass that writes the normalised row.
+constexpr int HC_MAX = 8;     // most streams
+
+template <typename OT, typename WT>
+__global__ void hc_add_rmsnorm_kernel(HyperNormArgs a) {
+  pdl_launch_dependents();
+  extern __shared__ float u_row[];               // [hidden]
+  __shared__ float red[32];
+  __shared__ float c_mix[HC_MAX * HC_MAX], c_write[HC_MAX], c_read[HC_MAX];
+  const int S = a.n_streams;
+  // the connection's weights are no result of this step: fetched while the kernel ahead still runs
+  if (threadIdx.x < S * S) c_mix[threadIdx.x] = a.branch ? a.mix[threadIdx.x] : 0.f;
+  if (threadIdx.x < S) {
+    c_write[threadIdx.x] = a.branch ? a.write[threadIdx.x] : 0.f;
+    c_read[threadIdx.x] = a.read ? a.read[threadIdx.x] : 1.f;
+  }
+  pdl_wait();
+  __syncthreads();
+  const int j = blockIdx.x;
+  const int r = a.rows ? a.rows[j] : j;
+  const int hidden = a.hidden;
+  float* base = a.streams + (long long)r * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float x[HC_MAX];
+#pragma unroll
+    for (int s = 0; s < HC_MAX; ++s) x[s] = s < S ? base[s * a.stream_stride + i] : 0.f;
+    if (a.branch) {
+      const float* b = a.branch + (long long)r * hidden + i;
+      float y = 0.f;
+      for (int p = 0; p < a.n_partials; ++p) y += b[p * a.partial_stride];
+      float nx[HC_MAX];
+#pragma unroll
+      for (int t = 0; t < HC_MAX; ++t) {
+        float v = 0.f;
+        if (t < S) {
+#pragma unroll
+          for (int s = 0; s < HC_MAX; ++s)
+            if (s < S) v = fmaf(c_mix[s * S + t], x[s], v);
+          v = fmaf(c_write[t], y, v);
+          base[t * a.stream_stride + i] = v;
+        }
+        nx[t] = v;
+      }
+#pragma unroll
+      for (int t = 0; t < HC_MAX; ++t) x[t] = nx[t];
+    }
+    float u = 0.f;
+#pragma unroll
+    for (int s = 0; s < HC_MAX; ++s)
+      if (s < S) u = fmaf(c_read[s], x[s], u);
+    u_row[i] = u;
+    ss += u * u;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)hidden + a.eps);
+  OT* o = (OT*)a.out + (long long)j * hidden;
+  const WT* w = (const WT*)a.weight;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<OT>(u_row[i] * inv * to_f32(w[i]));
+}
+
+LLG_API int llg_hc_max_streams() { return HC_MAX; }
+
+LLG_API int llg_hc_add_rmsnorm(const HyperNormArgs* args, cudaStream_t stream) {
+  const HyperNormArgs& a = *args;
+  LLG_REQUIRE(a.n_out >= 0 && a.hidden > 0, "hc_add_rmsnorm: bad sizes n_out=%d hidden=%d", a.n_out, a.hidden);
+  LLG_REQUIRE(a.n_streams >= 1 && a.n_streams <= HC_MAX, "hc_add_rmsnorm: %d streams, this kernel takes 1 to %d", a.n_streams, HC_MAX);
+  LLG_REQUIRE(a.eps > 0.f, "hc_add_rmsnorm: eps must be positive");
+  LLG_REQUIRE(!a.branch || (a.n_partials >= 1 && a.mix && a.write), "hc_add_rmsnorm: a branch needs partials, mix and write weights");
+  if (a.n_out == 0) return 0;
+  const size_t smem = (size_t)a.hidden * sizeof(float);
+  LLG_REQUIRE(smem <= 200 * 1024, "hc_add_rmsnorm: rows of %d elements do not fit shared memory", a.hidden);
+  const int threads = a.hidden >= 2048 ? 512 : (a.hidden >= 512 ? 256 : 128);
+#define LAUNCH(OT, WT)                                                                                              \
+  do {                                                                                                              \
+    if (smem > 48 * 1024) {                                                                                         \
+      cudaError_t e = cudaFuncSetAttribute(hc_add_rmsnorm_kernel<OT, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e != cudaSuccess) return llg_fail("hc_add_rmsnorm: shared memory %zu: %s", smem, cudaGetErrorString(e));   \
+    }                                                                                                               \
+    llg_launch(hc_add_rmsnorm_kernel<OT, WT>, a.n_out, threads, smem, stream, a);                                   \
+  } while (0)
+  if (a.out_dtype == LLG_F32 && a.weight_dtype == LLG_F32) LAUNCH(float, float);
+  else if (a.out_dtype == LLG_F32 && a.weight_dtype == LLG_BF16) LAUNCH(float, __nv_bfloat16);
+  else if (a.out_dtype == LLG_BF16 && a.weight_dtype == LLG_F32) LAUNCH(__nv_bfloat16, float);
+  else if (a.out_dtype == LLG_BF16 && a.weight_dtype == LLG_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else return llg_fail("hc_add_rmsnorm: unknown dtypes out=%d weight=%d", a.out_dtype, a.weight_dtype);
+#undef LAUNCH
+  return llg_check_launch("hc_add_rmsnorm");
+}
+
+// ---- queries, keys, values and gates from one product's row, norms over whole rows -------
+
+// See QkvRowPrepArgs in kernel_args.h.  One block per token; the summed row stays in shared memory.
+template <typename OT, typename WT>
+__global__ void qkv_row_prep_kernel(QkvRowPrepArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float row[];                 // [q | k | v | gates]
+  __shared__ float red[32];
+  const int n = blockIdx.x;
+  const int Q = a.nh * a.hd, K = a.nkv * a.hd, V = a.nkv * a.vd, G = a.gate_out ? a.nh : 0;
+  const int W = Q + K + V + G;
+  const float* src = a.qkvg + (long long)n * W;
+  const WT* bias = (const WT*)a.bias;
+  float ss_q = 0.f, ss_k = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    float v = 0.f;
+    for (int p = 0; p < a.n_partials; ++p) v += src[p * a.partial_stride + i];
+    if (bias && i < Q + K + V) v += to_f32(bias[i]);
+    row[i] = v;
+    if (i < Q) ss_q += v * v;
+    else if (i < Q + K) ss_k += v * v;
+  }
+  ss_q = block_sum(ss_q, red);
+  ss_k = block_sum(ss_k, red);
+  __syncthreads();
+  const float inv_q = a.q_norm_w ? 1.0f / sqrtf(ss_q / (float)Q + a.norm_eps) : 1.f;
+  const float inv_k = (a.k_norm_w && K > 0) ? 1.0f / sqrtf(ss_k / (float)K + a.norm_eps) : 1.f;
+  const WT* qw = (const WT*)a.q_norm_w;
+  const WT* kw = (const WT*)a.k_norm_w;
+  const int pos = a.positions[n];
+  const bool to_pages = a.k_pages != nullptr;
+  const int slot = to_pages ? a.slots[a.seq_of_token[n]] : 0;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float v = row[i];
+    if (i < Q) {
+      ((OT*)a.q_out)[(long long)n * Q + i] = from_f32<OT>(qw ? v * inv_q * to_f32(qw[i]) : v);
+    } else if (i < Q + K) {
+      const int c = i - Q;
+      const OT o = from_f32<OT>(kw ? v * inv_k * to_f32(kw[c]) : v);
+      if (a.k_new) ((OT*)a.k_new)[(long long)n * K + c] = o;
+      if (to_pages) {
+        const long long r = kv_row(a.page_table, a.table_width, a.ring_pages, slot, pos, c / a.hd, a.nkv);
+        ((OT*)a.k_pages)[r * a.hd + c % a.hd] = o;
+      }
+    } else if (i < Q + K + V) {
+      const int c = i - Q - K;
+      const OT o = from_f32<OT>(v);
+      if (a.v_new) ((OT*)a.v_new)[(long long)n * V + c] = o;
+      if (to_pages) {
+        const long long r = kv_row(a.page_table, a.table_width, a.ring_pages, slot, pos, c / a.vd, a.nkv);
+        ((OT*)a.v_pages)[r * a.vd + c % a.vd] = o;
+      }
+    } else {
+      a.gate_out[(long long)n * a.nh + (i - Q - K - V)] = 1.0f / (1.0f + expf(-v));
+    }
+  }
+}
+
+LLG_API int llg_qkv_row_prep(const QkvRowPrepArgs* args, int out_dtype, cudaStream_t stream) {
+  const QkvRowPrepArgs& a = *args;
+  LLG_REQUIRE(a.n_tokens >= 0 && a.nh > 0 && a.nkv >= 0 && a.hd > 0 && a.vd > 0, "qkv_row_prep: bad sizes");
+  LLG_REQUIRE(a.n_partials >= 1, "qkv_row_prep: n_partials must be >= 1");
+  LLG_REQUIRE(!a.k_pages || (a.v_pages && a.page_table && a.slots && a.seq_of_token && a.ring_pages > 0),
+              "qkv_row_prep: a cache write needs both page stores, page_table, slots and seq_of_token");
+  LLG_REQUIRE((a.k_new == nullptr) == (a.v_new == nullptr), "qkv_row_prep: packed keys and values go together");
+  if (a.n_tokens == 0) return 0;
+  const long long w = (long long)a.nh * a.hd + (long long)a.nkv * (a.hd + a.vd) + (a.gate_out ? a.nh : 0);
+  const size_t smem = (size_t)w * sizeof(float);
+  LLG_REQUIRE(smem <= 200 * 1024, "qkv_row_prep: rows of %lld elements do not fit shared memory", w);
+  const int threads = w >= 2048 ? 512 : 256;
+#define LAUNCH(OT, WT)                                                                                             \
+  do {                                                                                                             \
+    if (smem > 48 * 1024) {                                                                                        \
+      cudaError_t e = cudaFuncSetAttribute(qkv_row_prep_kernel<OT, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e != cudaSuccess) return llg_fail("qkv_row_prep: shared memory %zu: %s", smem, cudaGetErrorString(e));    \
+    }                                                                                                              \
+    llg_launch(qkv_row_prep_kernel<OT, WT>, a.n_tokens, threads, smem, stream, a);                                 \
+  } while (0)
+  if (out_dtype == LLG_F32 && a.w_dtype == LLG_F32) LAUNCH(float, float);
+  else if (out_dtype == LLG_F32 && a.w_dtype == LLG_BF16) LAUNCH(float, __nv_bfloat16);
+  else if (out_dtype == LLG_BF16 && a.w_dtype == LLG_F32) LAUNCH(__nv_bfloat16, float);
+  else if (out_dtype == LLG_BF16 && a.w_dtype == LLG_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else return llg_fail("qkv_row_prep: unknown dtypes out=%d weights=%d", out_dtype, a.w_dtype);
+#undef LAUNCH
+  return llg_check_launch("qkv_row_prep");
+}
+
+// ---- activations of an ungated feed-forward ---------------------------------------------
+
+// out[n][i] = act(sum of the partials of in[n][i]).  Kinds: 0 relu(z)^2, 1 gelu with the tanh form
+// 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), 2 silu, 3 relu.
+__device__ __forceinline__ float llg_act(int kind, float z) {
+  switch (kind) {
+    case 0: { const float r = fmaxf(z, 0.f); return r * r; }
+    case 1: return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    case 2: return z / (1.0f + expf(-z));
+    default: return fmaxf(z, 0.f);
+  }
+}
+
+template <typename IT, typename OT>
+__global__ void act_rows_kernel(const IT* __restrict__ in, int n_partials, long long partial_stride, OT* __restrict__ out,
+                                long long total, int kind) {
+  pdl_launch_dependents();
+  pdl_wait();
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (long long)gridDim.x * blockDim.x) {
+    float z = 0.f;
+    for (int s = 0; s < n_partials; ++s) z += to_f32(in[s * partial_stride + idx]);
+    out[idx] = from_f32<OT>(llg_act(kind, z));
+  }
+}
+
+LLG_API int llg_act_rows(const void* in, int in_dtype, int n_partials, long long partial_stride, void* out, int out_dtype,
+                         long long total, int kind, cudaStream_t stream) {
+  LLG_REQUIRE(total >= 0 && n_partials >= 1 && kind >= 0 && kind <= 3, "act_rows: bad arguments");
+  if (total == 0) return 0;
+  const int threads = 256;
+  long long blocks = (total + threads - 1) / threads;
+  if (blocks > (long long)llg_sm_count() * 16) blocks = (long long)llg_sm_count() * 16;
+#define LAUNCH(IT, OT) \
+  llg_launch(act_rows_kernel<IT, OT>, (unsigned)blocks, threads, 0, stream, (const IT*)in, n_partials, partial_stride, (OT*)out, total, kind)
+  if (in_dtype == LLG_F32 && out_dtype == LLG_F32) LAUNCH(float, float);
+  else if (in_dtype == LLG_F32 && out_dtype == LLG_BF16) LAUNCH(float, __nv_bfloat16);
+  else if (in_dtype == LLG_BF16 && out_dtype == LLG_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  else return llg_fail("act_rows: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
+#undef LAUNCH
+  return llg_check_launch("act_rows");
+}

@@ -81,6 +81,12 @@ struct PrefillArgs {
   float scale;
   int window;               // 0 = all keys
   int n_tokens, n_pages;    // rows of k_new / v_new, pages of k_pages / v_pages
+  // Further forms of attention; all zero gives the plain one.  Only the kernels of attention_simt.cu and attention_mma.cu
+  // read these (a caller checks with the library's *_supported function before it sets them for another kernel).
+  int vd;                   // elements of a value head (v_new, v_pages and out then have vd where they say hd); 0 = hd
+  int has_sink;             // 1: a sink of score sink_score joins every softmax's denominator and carries no value
+  float sink_score;
+  const float* gate;        // [n_tokens][nh] or null: a head's output is multiplied by its token's gate
 };
 
 // Attention of one new token per sequence, split kernels (attention_simt.cu, attention_mma.cu).
@@ -98,6 +104,10 @@ struct DecodeArgs {
   int n_seqs, nh, nkv, hd, n_splits;
   float scale;
   int window;
+  int vd;                   // as in PrefillArgs; part_o then is [B][nh][n_splits][vd]
+  int has_sink;
+  float sink_score;
+  const float* gate;        // [B][nh] or null
 };
 
 // Attention of one new token per sequence, TMA kernel (attention_decode_tma.cu).
@@ -114,4 +124,59 @@ struct DecodeTmaArgs {
   int n_seqs, nh, nkv, hd;
   float scale;
   int window;
+};
+
+// Residual kept as several streams (hyper-connections), elementwise.cu: hc_add_rmsnorm.  For output row j (token
+// r = rows ? rows[j] : j), with S streams X_s of width `hidden`:
+//   y = sum of the branch's partials                        (when there is a branch)
+//   X_t <- sum_s mix[s][t] X_s + write[t] * y               (all streams at once from the old ones; written back)
+//   u = sum_s read[s] X_s   (read == null: the plain sum)
+//   out[j] = u / sqrt(mean(u^2) + eps) * weight
+// The streams, the small vectors and all sums are float32.
+struct HyperNormArgs {
+  float* streams;             // [S][n_tokens][hidden]
+  long long stream_stride;    // elements between streams
+  int n_streams;
+  const float* branch;        // [n_partials][n_tokens][hidden] or null
+  int n_partials;
+  long long partial_stride;
+  const float* mix;           // [S][S], indexed [from][to]; with a branch
+  const float* write;         // [S]; with a branch
+  const float* read;          // [S] or null
+  const void* weight;         // [hidden]
+  int weight_dtype;
+  float eps;
+  void* out;                  // [n_out][hidden]
+  int out_dtype;
+  const int* rows;            // [n_out] or null
+  int n_out, hidden;
+};
+
+// Preparation of queries, keys, values and head gates from one product's row (elementwise.cu: qkv_row_prep).  A row
+// of the product holds q [nh * hd], k [nkv * hd], v [nkv * vd] and, with gates, one more number per query head.  Per
+// token: partial sums added, biases added, then an RMS norm over the WHOLE q part and one over the whole k part (each
+// with a weight vector of the part's size; null = none); q, k and v are written as qk_prep writes them (packed and/or
+// into the cache pages) and the gates as sigmoid(g) in float32.
+struct QkvRowPrepArgs {
+  const float* qkvg;          // [n_partials][n_tokens][row]
+  int n_partials;
+  long long partial_stride;
+  const void* bias;           // [nh * hd + nkv * hd + nkv * vd] or null (the gates have none)
+  const void* q_norm_w;       // [nh * hd] or null
+  const void* k_norm_w;       // [nkv * hd] or null
+  int w_dtype;                // of bias and norm weights
+  float norm_eps;
+  const int* positions;       // [n_tokens]
+  void* q_out;                // [n_tokens][nh][hd]
+  void* k_new;                // [n_tokens][nkv][hd] or null
+  void* v_new;                // [n_tokens][nkv][vd] or null
+  void* k_pages;              // paged store or null
+  void* v_pages;
+  const int* page_table;
+  int table_width;
+  int ring_pages;
+  const int* seq_of_token;
+  const int* slots;
+  float* gate_out;            // [n_tokens][nh] or null (the row then has no gate part)
+  int n_tokens, nh, nkv, hd, vd;
 };

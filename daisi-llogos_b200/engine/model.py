@@ -19,6 +19,8 @@ from ..parts import attention as _attention  # noqa: F401
 from ..parts.block import normed_for
 from ..parts import embedding as _embedding  # noqa: F401
 from ..parts import feedforward as _feedforward  # noqa: F401
+from ..parts import gated_attention as _gated_attention  # noqa: F401
+from ..parts import hyper as _hyper  # noqa: F401
 from ..parts import norm as _norm  # noqa: F401
 from ..parts import position as _position  # noqa: F401
 
@@ -81,7 +83,7 @@ class DecoderModel:
         decls: Dict[str, TensorDecl] = {}
         for p in self._all_parts():
             for rel, d in p.tensors().items():
-                name = p.prefix + rel
+                name = p.tensor_name(rel)
                 if name in decls:
                     raise ValueError(f"tensor '{name}' is declared by two parts")
                 decls[name] = d
@@ -89,7 +91,7 @@ class DecoderModel:
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         for p in self._all_parts():
-            mine = {rel: tensors[p.prefix + rel] for rel in p.tensors() if (p.prefix + rel) in tensors}
+            mine = {rel: tensors[p.tensor_name(rel)] for rel in p.tensors() if p.tensor_name(rel) in tensors}
             tied = getattr(p, "tied_to", None)
             if tied:
                 mine["weight"] = tensors[tied]

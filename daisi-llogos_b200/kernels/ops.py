@@ -135,6 +135,7 @@ class _PrefillArgs(Structure):
         ("out", c_void_p),
         ("n_tiles", c_int), ("nh", c_int), ("nkv", c_int), ("hd", c_int),
         ("scale", c_float), ("window", c_int), ("n_tokens", c_int), ("n_pages", c_int),
+        ("vd", c_int), ("has_sink", c_int), ("sink_score", c_float), ("gate", c_void_p),
     ]
 
 
@@ -145,6 +146,28 @@ class _DecodeArgs(Structure):
         ("part_o", c_void_p), ("part_ml", c_void_p),
         ("n_seqs", c_int), ("nh", c_int), ("nkv", c_int), ("hd", c_int), ("n_splits", c_int),
         ("scale", c_float), ("window", c_int),
+        ("vd", c_int), ("has_sink", c_int), ("sink_score", c_float), ("gate", c_void_p),
+    ]
+
+
+class _HyperNormArgs(Structure):
+    _fields_ = [
+        ("streams", c_void_p), ("stream_stride", c_longlong), ("n_streams", c_int),
+        ("branch", c_void_p), ("n_partials", c_int), ("partial_stride", c_longlong),
+        ("mix", c_void_p), ("write", c_void_p), ("read", c_void_p),
+        ("weight", c_void_p), ("weight_dtype", c_int), ("eps", c_float),
+        ("out", c_void_p), ("out_dtype", c_int), ("rows", c_void_p), ("n_out", c_int), ("hidden", c_int),
+    ]
+
+
+class _QkvRowPrepArgs(Structure):
+    _fields_ = [
+        ("qkvg", c_void_p), ("n_partials", c_int), ("partial_stride", c_longlong),
+        ("bias", c_void_p), ("q_norm_w", c_void_p), ("k_norm_w", c_void_p), ("w_dtype", c_int), ("norm_eps", c_float),
+        ("positions", c_void_p), ("q_out", c_void_p), ("k_new", c_void_p), ("v_new", c_void_p),
+        ("k_pages", c_void_p), ("v_pages", c_void_p), ("page_table", c_void_p), ("table_width", c_int),
+        ("ring_pages", c_int), ("seq_of_token", c_void_p), ("slots", c_void_p), ("gate_out", c_void_p),
+        ("n_tokens", c_int), ("nh", c_int), ("nkv", c_int), ("hd", c_int), ("vd", c_int),
     ]
 
 
@@ -205,6 +228,9 @@ def _load_lib(name: str):
         lib.llg_scatter_i32.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p]
         lib.llg_gather_i32.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p]
         lib.llg_zero_rows.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_void_p]
+        lib.llg_hc_add_rmsnorm.argtypes = [POINTER(_HyperNormArgs), c_void_p]
+        lib.llg_qkv_row_prep.argtypes = [POINTER(_QkvRowPrepArgs), c_int, c_void_p]
+        lib.llg_act_rows.argtypes = [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_longlong, c_int, c_void_p]
     elif name == "gemm_simt":
         lib.llg_gemm_simt.argtypes = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                                       POINTER(_RowScale), c_void_p]
@@ -478,12 +504,106 @@ def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, *, n_heads: int, n_kv_heads: i
     _check(lib, lib.llg_gemm_tc_qkv(_ptr(x, torch.bfloat16), _ptr(w, torch.bfloat16), n, k, byref(a), _stream()))
 
 
+def hc_max_streams() -> int:
+    """Most residual streams ``hc_add_rmsnorm`` takes."""
+    return _lib("elementwise").llg_hc_max_streams()
+
+
+def hc_add_rmsnorm(streams: torch.Tensor, branch: Optional[torch.Tensor], mix: Optional[torch.Tensor],
+                   write: Optional[torch.Tensor], read: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                   out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """The residual as ``S`` streams (float32 ``[S, N, H]``): with a branch (float32 partials ``[P, N, H]``, summed to y)
+    every stream becomes ``X_t = sum_s mix[s, t] X_s + write[t] y`` (all at once from the old ones, written back); then
+    ``u = sum_s read[s] X_s`` (``read`` None: the plain sum) and ``out[j] = RMSNorm(u[rows[j] or j]) * weight``.
+    ``mix`` ``[S, S]``, ``write`` and ``read`` ``[S]`` are float32."""
+    lib = _lib("elementwise")
+    s_n, n, hidden = streams.shape
+    m = out.shape[0]
+    assert out.shape[1] == hidden and weight.shape == (hidden,)
+    assert rows.numel() == m if rows is not None else m == n
+    a = _HyperNormArgs()
+    a.streams, a.stream_stride, a.n_streams = _ptr(streams, torch.float32), n * hidden, s_n
+    if branch is not None:
+        assert branch.dim() == 3 and branch.shape[1:] == (n, hidden), (branch.shape, streams.shape)
+        assert mix.shape == (s_n, s_n) and write.shape == (s_n,)
+        a.branch, a.n_partials, a.partial_stride = _ptr(branch, torch.float32), branch.shape[0], n * hidden
+        a.mix, a.write = _ptr(mix, torch.float32), _ptr(write, torch.float32)
+    if read is not None:
+        assert read.shape == (s_n,)
+        a.read = _ptr(read, torch.float32)
+    a.weight, a.weight_dtype, a.eps = _ptr(weight), _dt(weight), float(eps)
+    a.out, a.out_dtype, a.rows, a.n_out, a.hidden = _ptr(out), _dt(out), _ptr(rows, torch.int32), m, hidden
+    _check(lib, lib.llg_hc_add_rmsnorm(byref(a), _stream()))
+
+
+def qkv_row_prep(qkvg: torch.Tensor, *, n_heads: int, n_kv_heads: int, head_dim: int, value_dim: int,
+                 bias: Optional[torch.Tensor], q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor],
+                 norm_eps: float, positions: torch.Tensor, q_out: torch.Tensor, gate_out: Optional[torch.Tensor] = None,
+                 k_new: Optional[torch.Tensor] = None, v_new: Optional[torch.Tensor] = None,
+                 k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
+                 page_table: Optional[torch.Tensor] = None, ring_pages: int = 0,
+                 seq_of_token: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None) -> None:
+    """Queries, keys, values and head gates from the rows of one product, float32 partials ``[P, N, row]`` with
+    ``row = nh hd + nkv hd + nkv vd (+ nh gates)``: partials summed, ``bias`` added (q, k and v parts), an RMS norm over
+    the whole q part and one over the whole k part (weights of those sizes; None = none), then the writes of
+    ``qk_prep`` (values ``[N, nkv, vd]``) and ``gate_out[n, h] = sigmoid(g)`` in float32."""
+    lib = _lib("elementwise")
+    p_n, n, width = qkvg.shape
+    q_w, k_w, v_w = n_heads * head_dim, n_kv_heads * head_dim, n_kv_heads * value_dim
+    assert width == q_w + k_w + v_w + (n_heads if gate_out is not None else 0), (width, q_w, k_w, v_w)
+    ws = [t for t in (bias, q_norm_w, k_norm_w) if t is not None]
+    if len({t.dtype for t in ws}) > 1:
+        raise KernelError("qkv_row_prep: bias and norm weights must share a dtype")
+    for t in (k_new, v_new, k_pages, v_pages):
+        if t is not None and t.dtype != q_out.dtype:
+            raise KernelError("qkv_row_prep: all outputs must share one dtype")
+    a = _QkvRowPrepArgs()
+    a.qkvg, a.n_partials, a.partial_stride = _ptr(qkvg, torch.float32), p_n, n * width
+    a.bias, a.q_norm_w, a.k_norm_w = _ptr(bias), _ptr(q_norm_w), _ptr(k_norm_w)
+    a.w_dtype = _dt(ws[0]) if ws else F32
+    a.norm_eps = float(norm_eps)
+    a.positions = _ptr(positions, torch.int32)
+    a.q_out, a.k_new, a.v_new = _ptr(q_out), _ptr(k_new), _ptr(v_new)
+    a.k_pages, a.v_pages = _ptr(k_pages), _ptr(v_pages)
+    if page_table is not None:
+        a.page_table, a.table_width = _ptr(page_table, torch.int32), page_table.shape[1]
+    a.ring_pages = ring_pages
+    a.seq_of_token, a.slots = _ptr(seq_of_token, torch.int32), _ptr(slots, torch.int32)
+    a.gate_out = _ptr(gate_out, torch.float32)
+    a.n_tokens, a.nh, a.nkv, a.hd, a.vd = n, n_heads, n_kv_heads, head_dim, value_dim
+    _check(lib, lib.llg_qkv_row_prep(byref(a), _dt(q_out), _stream()))
+
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+
+
+def act_rows(x: torch.Tensor, out: torch.Tensor, kind: str) -> None:
+    """out[n, i] = act(sum of the partials ``x[:, n, i]``); ``kind`` is one of ``ACTIVATIONS``: relu2 (the square of
+    relu), gelu_tanh, silu, relu."""
+    lib = _lib("elementwise")
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"act_rows: activation '{kind}' is not known ({', '.join(ACTIVATIONS)})")
+    p_n, n, width = x.shape
+    assert out.shape == (n, width)
+    _check(lib, lib.llg_act_rows(_ptr(x), _dt(x), p_n, n * width, _ptr(out), _dt(out), n * width, ACTIVATIONS[kind], _stream()))
+
+
 def kv_write(k_new, v_new, k_pages, v_pages, page_table, ring_pages, positions, seq_of_token, slots,
              cu_tokens, len_before) -> None:
-    """Copies a prompt step's packed keys/values ``[N, nkv, hd]`` into the cache pages."""
+    """Copies a prompt step's packed keys/values ``[N, nkv, hd]`` into the cache pages (values may have another
+    head size than keys)."""
     lib = _lib("elementwise")
     n, nkv, hd = k_new.shape
     assert k_pages.dtype == k_new.dtype == v_new.dtype == v_pages.dtype
+    if v_new.shape[2] != hd:
+        # two passes of the same kernel, each with keys and values of one size
+        for src, dst in ((k_new, k_pages), (v_new, v_pages)):
+            _check(lib, lib.llg_kv_write(_ptr(src), _ptr(src), _ptr(dst), _ptr(dst),
+                                         _ptr(page_table, torch.int32), page_table.shape[1], ring_pages,
+                                         _ptr(positions, torch.int32), _ptr(seq_of_token, torch.int32),
+                                         _ptr(slots, torch.int32), _ptr(cu_tokens, torch.int32),
+                                         _ptr(len_before, torch.int32), n, nkv, src.shape[2], _dt(src), _stream()))
+        return
     _check(lib, lib.llg_kv_write(_ptr(k_new), _ptr(v_new), _ptr(k_pages), _ptr(v_pages),
                                  _ptr(page_table, torch.int32), page_table.shape[1], ring_pages,
                                  _ptr(positions, torch.int32), _ptr(seq_of_token, torch.int32),
@@ -538,11 +658,42 @@ def _use_tc_attn(dtype: torch.dtype, head_dim: int) -> bool:
     return USE_TC_PROMPT_ATTENTION and dtype == torch.bfloat16 and head_dim in (64, 128)
 
 
-def prefill_tile_queries(dtype: torch.dtype, head_dim: int) -> int:
+class AttentionForm:
+    """What an attention computes beyond the plain causal softmax over keys and values of one head size:
+    ``value_dim`` (elements of a value head; 0 = the key heads' size), ``sink`` (None, or the score of a sink that
+    joins every softmax's denominator and carries no value: ``p_j = e^{s_j} / (e^{sink} + sum e^{s_j})``), ``gated``
+    (the output of every (token, head) is multiplied by a float32 gate ``[N, nh]`` that the caller passes)."""
+
+    def __init__(self, value_dim: int = 0, sink: Optional[float] = None, gated: bool = False):
+        self.value_dim, self.sink, self.gated = int(value_dim), (None if sink is None else float(sink)), bool(gated)
+
+    def plain(self, head_dim: int) -> bool:
+        return self.value_dim in (0, head_dim) and self.sink is None and not self.gated
+
+    def vd(self, head_dim: int) -> int:
+        return self.value_dim or head_dim
+
+
+PLAIN_ATTENTION = AttentionForm()
+
+
+def _prefill_kernel(dtype: torch.dtype, head_dim: int, form: AttentionForm) -> str:
+    """Which prompt attention kernel takes this geometry and form."""
+    if form.plain(head_dim):
+        return "tc" if _use_tc_attn(dtype, head_dim) else "mma" if _use_mma(dtype, head_dim) else "simt"
+    return "simt"
+
+
+def prefill_tile_queries(dtype: torch.dtype, head_dim: int, form: AttentionForm = PLAIN_ATTENTION) -> int:
     """Queries per block of the prompt attention kernel that ``attn_prefill`` will run."""
-    if _use_tc_attn(dtype, head_dim):
-        return 256
-    return 64 if _use_mma(dtype, head_dim) else 16
+    return {"tc": 256, "mma": 64, "simt": 16}[_prefill_kernel(dtype, head_dim, form)]
+
+
+def _set_form(a, form: AttentionForm, head_dim: int, gate: Optional[torch.Tensor]) -> None:
+    """The fields of a prompt or decode argument block that say which form of attention is wanted."""
+    a.vd = 0 if form.value_dim in (0, head_dim) else form.value_dim
+    a.has_sink, a.sink_score = (0, 0.0) if form.sink is None else (1, form.sink)
+    a.gate = _ptr(gate, torch.float32)
 
 
 def attn_tc_status() -> int:
@@ -551,25 +702,30 @@ def attn_tc_status() -> int:
 
 
 def attn_prefill(q, k_new, v_new, k_pages, v_pages, page_table, ring_pages, tiles, cu_tokens, len_before,
-                 slots, out, *, scale: float, window: int, tile_queries: int) -> None:
+                 slots, out, *, scale: float, window: int, tile_queries: int,
+                 form: AttentionForm = PLAIN_ATTENTION, gate: Optional[torch.Tensor] = None) -> None:
     """Causal attention for a step with several tokens per sequence.
 
     ``tiles`` is ``[n_tiles, 2]`` (sequence index, first query among its step tokens) cut every
     ``tile_queries`` queries, which must be ``prefill_tile_queries(q.dtype, head_dim)``.  bfloat16 runs on
     the tensor cores: head sizes 64 and 128 with tcgen05 (csrc/attention_tc.cu), other multiples of 16 up
     to 128 with mma.sync (csrc/attention_mma.cu); everything else on the CUDA cores
-    (csrc/attention_simt.cu).
+    (csrc/attention_simt.cu).  ``form`` (an ``AttentionForm``) and ``gate`` ask for values of another head size, a
+    sink and gated heads; ``out`` is then ``[N, nh * value_dim]``.
     """
     n, nh, hd = q.shape
     nkv = k_new.shape[1]
-    assert out.shape == (n, nh * hd)
-    if tile_queries != prefill_tile_queries(q.dtype, hd):
+    vd = form.vd(hd)
+    assert out.shape == (n, nh * vd) and v_new.shape == (k_new.shape[0], nkv, vd) and v_pages.shape[3] == vd
+    if tile_queries != prefill_tile_queries(q.dtype, hd, form):
         raise KernelError(f"attn_prefill: tiles of {tile_queries} queries, the kernel works on "
-                          f"{prefill_tile_queries(q.dtype, hd)}")
+                          f"{prefill_tile_queries(q.dtype, hd, form)}")
     if scale <= 0:
         raise KernelError("attn_prefill: the softmax scale must be positive")
-    tc = _use_tc_attn(q.dtype, hd)
-    mma = _use_mma(q.dtype, hd)
+    if form.gated != (gate is not None) or (gate is not None and tuple(gate.shape) != (n, nh)):
+        raise KernelError("attn_prefill: a gated form needs a gate [tokens, heads], and only a gated form takes one")
+    kernel = _prefill_kernel(q.dtype, hd, form)
+    tc, mma = kernel == "tc", kernel == "mma"
     lib = _lib("attention_tc" if tc else "attention_mma" if mma else "attention_simt")
     a = _PrefillArgs()
     a.q, a.k_new, a.v_new = _ptr(q), _ptr(k_new, q.dtype), _ptr(v_new, q.dtype)
@@ -581,6 +737,7 @@ def attn_prefill(q, k_new, v_new, k_pages, v_pages, page_table, ring_pages, tile
     a.n_tiles, a.nh, a.nkv, a.hd = tiles.shape[0], nh, nkv, hd
     a.scale, a.window = float(scale), int(window)
     a.n_tokens, a.n_pages = k_new.shape[0], k_pages.shape[0]
+    _set_form(a, form, hd, gate)
     if tc:
         _check(lib, lib.llg_attn_prefill_tc(byref(a), _stream()))
     elif mma:
@@ -627,19 +784,22 @@ def _splits_for(n_seqs: int, n_kv_heads: int, max_len: int, n_sms: int, blocks_p
     return best
 
 
-def attn_decode_plan(dtype: torch.dtype, n_seqs: int, n_heads: int, n_kv_heads: int, head_dim: int, max_len: int) -> DecodePlan:
+def attn_decode_plan(dtype: torch.dtype, n_seqs: int, n_heads: int, n_kv_heads: int, head_dim: int, max_len: int,
+                     form: AttentionForm = PLAIN_ATTENTION) -> DecodePlan:
     """The plan for a batch of ``n_seqs`` sequences of at most ``max_len`` keys (the new token's included).
 
     bfloat16 at head sizes 64 / 128: the TMA kernel, which balances the work itself from the lengths it finds on
     the device.  Other multiples of 16 up to 128: the mma.sync kernel with a split count from ``max_len`` (per
-    sequence by its length for small batches).  Everything else: the CUDA-core kernel."""
-    if _use_tma_decode(dtype, head_dim, n_heads, n_kv_heads, n_seqs):
+    sequence by its length for small batches).  Everything else, and every form but the plain one: the CUDA-core
+    kernel."""
+    plain = form.plain(head_dim)
+    if plain and _use_tma_decode(dtype, head_dim, n_heads, n_kv_heads, n_seqs):
         lib = _lib("attention_decode_tma")
         floats = lib.llg_attn_decode_tma_scratch_floats(n_seqs, n_heads, n_kv_heads, head_dim, max_len)
         return DecodePlan("tma", 0, False, max_len, int(floats), n_seqs * n_heads)
     n_sms = sm_count()
     splits = _splits_for(n_seqs, n_kv_heads, max_len, n_sms)
-    mma = _use_mma(dtype, head_dim)
+    mma = plain and _use_mma(dtype, head_dim)
     # Sequences of unequal lengths: the kernel gives each as many splits as its length calls for, up to what
     # one long sequence among short ones could use (the blocks the GPU holds, less one per other pair).
     balance = mma and 1 < n_seqs <= 32 and n_seqs * n_kv_heads <= attn_decode_balance_pairs()
@@ -647,7 +807,7 @@ def attn_decode_plan(dtype: torch.dtype, n_seqs: int, n_heads: int, n_kv_heads: 
         tiles = max(1, -(-max_len // PAGE))
         splits = max(splits, min(64, tiles, 2 * n_sms // n_kv_heads - (n_seqs - 1)))
     return DecodePlan("mma" if mma else "simt", splits, balance, max_len,
-                      attn_decode_scratch_floats(n_seqs, n_heads, head_dim, splits), n_seqs * n_kv_heads if mma else 0)
+                      attn_decode_scratch_floats(n_seqs, n_heads, form.vd(head_dim), splits), n_seqs * n_kv_heads if mma else 0)
 
 
 def attn_decode_scratch_floats(n_seqs: int, n_heads: int, head_dim: int, n_splits: int) -> int:
@@ -673,7 +833,8 @@ def attn_decode_tma_status() -> int:
 
 def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, out, scratch, *,
                 scale: float, window: int, plan: Optional[DecodePlan] = None, n_splits: int = 0,
-                counters: Optional[torch.Tensor] = None, balance: bool = False) -> None:
+                counters: Optional[torch.Tensor] = None, balance: bool = False,
+                form: AttentionForm = PLAIN_ATTENTION, gate: Optional[torch.Tensor] = None) -> None:
     """Attention of one new token per sequence over the cache; ``scratch`` holds the partial results.
 
     With ``plan`` (from ``attn_decode_plan`` for this batch shape) the kernel is the plan's.  Without it the
@@ -687,10 +848,16 @@ def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, 
     ``n_splits`` is the most splits a sequence may have; each gets as many as its length calls for."""
     b, nh, hd = q.shape
     nkv = k_pages.shape[1]
+    vd = form.vd(hd)
     if scale <= 0:
         raise KernelError("attn_decode: the softmax scale must be positive")
     if scratch.dtype != torch.float32:
         raise KernelError("attn_decode: the scratch must be float32")
+    if form.gated != (gate is not None) or (gate is not None and tuple(gate.shape) != (b, nh)):
+        raise KernelError("attn_decode: a gated form needs a gate [sequences, heads], and only a gated form takes one")
+    if not form.plain(hd) and plan is not None and plan.kind != "simt":
+        raise KernelError(f"attn_decode: the {plan.kind} kernel computes the plain form only")
+    assert out.shape == (b, nh * vd) and v_pages.shape[3] == vd
     if plan is not None and plan.kind == "tma":
         lib = _lib("attention_decode_tma")
         if scratch.numel() < plan.scratch_floats:
@@ -709,9 +876,9 @@ def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, 
         return
     if plan is not None:
         n_splits, balance = plan.n_splits, plan.balance
-    mma = _use_mma(q.dtype, hd)
+    mma = form.plain(hd) and _use_mma(q.dtype, hd)
     lib = _lib("attention_mma" if mma else "attention_simt")
-    need = b * nh * n_splits * (hd + 2)
+    need = b * nh * n_splits * (vd + 2)
     if n_splits < 1 or scratch.numel() < need:
         raise KernelError(f"attn_decode: {n_splits} splits, scratch of {scratch.numel()} floats, {need} needed")
     a = _DecodeArgs()
@@ -720,9 +887,10 @@ def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, 
     a.slots, a.len_before = _ptr(slots, torch.int32), _ptr(len_before, torch.int32)
     base = _ptr(scratch)
     a.part_o = base
-    a.part_ml = base + 4 * b * nh * n_splits * hd
+    a.part_ml = base + 4 * b * nh * n_splits * vd
     a.n_seqs, a.nh, a.nkv, a.hd, a.n_splits = b, nh, nkv, hd, n_splits
     a.scale, a.window = float(scale), int(window)
+    _set_form(a, form, hd, gate)
     if mma:
         if counters is None or counters.numel() < b * nkv:
             raise KernelError(f"attn_decode: needs {b * nkv} zeroed int32 counters")

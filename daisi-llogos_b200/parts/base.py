@@ -35,7 +35,7 @@ class TensorDecl:
     """A tensor a part needs: its shape and what it is (decides random initialisation)."""
 
     shape: Tuple[int, ...]
-    role: str = "matrix"       # "matrix" | "norm" | "bias" | "table"
+    role: str = "matrix"       # "matrix" | "norm" | "bias" | "table" | "stream_gain" | "stream_mix"
     optional: bool = False
 
 
@@ -44,10 +44,13 @@ class Branch:
     """Output of a mixer or feed-forward that has not been added to the residual stream yet.
 
     ``data`` is ``[n_partials, n_tokens, hidden]``; the partials (split-K slices of a
-    matrix product, in float32) are summed by whoever consumes the branch.
+    matrix product, in float32) are summed by whoever consumes the branch.  ``write``: for a residual that is
+    more than one stream, the part that holds the weights with which this branch enters the streams (set by the
+    block that arranged the sublayer; ``None`` where the branch is simply added).
     """
 
     data: torch.Tensor
+    write: Any = None
 
     @property
     def n_partials(self) -> int:
@@ -56,11 +59,13 @@ class Branch:
 
 @dataclass(frozen=True)
 class KvNeed:
-    """A mixer keeps keys and values per position: ``window`` = 0 for all of them."""
+    """A mixer keeps keys and values per position: ``window`` = 0 for all of them; ``value_dim`` = 0 for value
+    heads of the key heads' size."""
 
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    value_dim: int = 0
 
 
 @dataclass(frozen=True)
@@ -82,6 +87,12 @@ class Part:
     def tensors(self) -> Dict[str, TensorDecl]:
         """Tensor name (relative to the prefix) -> declaration."""
         return {}
+
+    def tensor_name(self, rel: str) -> str:
+        """The name under which a checkpoint stores the tensor this part calls ``rel``: the prefix and ``rel``,
+        or what the part's ``tensor_names`` parameter says instead of ``rel`` (checkpoints of other families
+        name a norm's weight or a projection's matrix in their own way)."""
+        return self.prefix + self.params.get("tensor_names", {}).get(rel, rel)
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         """Receive the loaded tensors (same relative names); fuse or re-lay-out here."""
@@ -174,7 +185,7 @@ class BuildEnv:
 
 
 _REGISTRIES: Dict[str, Dict[str, Callable]] = {
-    "norm": {}, "mixer": {}, "ffn": {}, "position": {}, "block": {}, "embedding": {}, "head": {},
+    "norm": {}, "mixer": {}, "ffn": {}, "position": {}, "block": {}, "embedding": {}, "head": {}, "connection": {},
 }
 
 

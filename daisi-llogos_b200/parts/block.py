@@ -13,7 +13,7 @@ from .base import Block, Branch, register_part
 
 
 class PreNormBlock(Block):
-    """roles: norm1, mixer, norm2, ffn."""
+    """roles: norm1, mixer, norm2, ffn (a layer without a feed-forward leaves norm2 and ffn out)."""
 
     ROLES = {"norm1": "norm", "mixer": "mixer", "norm2": "norm", "ffn": "ffn"}
 
@@ -21,6 +21,8 @@ class PreNormBlock(Block):
         p = self.parts
         h, kw = normed_for(p["norm1"], p["mixer"], residual, pending, ctx)
         a = p["mixer"].forward(h, ctx, cache, **kw)
+        if "ffn" not in p:
+            return a
         h, kw = normed_for(p["norm2"], p["ffn"], residual, a, ctx)
         return p["ffn"].forward(h, ctx, **kw)
 

@@ -14,12 +14,14 @@ from .base import Part, TensorDecl, register_part
 
 
 class TokenEmbedding(Part):
-    """params: vocab_size, hidden_size."""
+    """params: vocab_size, hidden_size, streams (0: the residual is one ``[N, hidden]`` array; S >= 1: it is S
+    streams ``[S, N, hidden]`` that all start as the embedding)."""
 
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
         self.vocab = int(params["vocab_size"])
         self.hidden = int(params["hidden_size"])
+        self.streams = int(params.get("streams", 0) or 0)
         self.weight = None
 
     def tensors(self):
@@ -29,6 +31,11 @@ class TokenEmbedding(Part):
         self.weight = tensors["weight"]
 
     def forward(self, ctx) -> torch.Tensor:
+        if self.streams:
+            residual = ctx.buffer("residual", (self.streams, ctx.n_tokens, self.hidden), torch.float32)
+            for s in range(self.streams):
+                ctx.ops.embed_rows(self.weight, ctx.token_ids, residual[s])
+            return residual
         residual = ctx.buffer("residual", (ctx.n_tokens, self.hidden), torch.float32)
         ctx.ops.embed_rows(self.weight, ctx.token_ids, residual)
         return residual

@@ -1,4 +1,4 @@
-"""Feed-forward parts.
+"""Feed-forward parts: the gated ``SwiGLU`` and the ungated ``DenseMLP`` (up, activation, down).
 
 ``SwiGLU``: ``down( silu(gate(x)) * up(x) )`` without biases
 (Inference/ForwardPass.cs:242-246; silu(g) = g / (1 + exp(-g)), Daisi.Llogos.Cpu/Silu.cs:9-16).
@@ -45,4 +45,35 @@ class SwiGLU(FeedForward):
         return Branch(linear(ctx, act, self.w_down, "ffn.out", torch.float32))
 
 
+class DenseMLP(FeedForward):
+    """``down(act(up(x)))`` without a gate and without biases.  params: hidden_size, intermediate_size, activation
+    (one of ``ops.ACTIVATIONS``: "relu2" = the square of relu, "gelu_tanh", "silu", "relu").  The up product leaves
+    float32 sums (in parts when it splits them); one kernel adds them up, applies the activation and rounds to the
+    compute type once."""
+
+    def __init__(self, params, prefix, env):
+        super().__init__(params, prefix, env)
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.activation = str(params["activation"])
+        known = getattr(env.ops, "ACTIVATIONS", None)
+        if known is not None and self.activation not in known:
+            raise ValueError(f"dense_mlp: activation '{self.activation}' is not known ({', '.join(known)})")
+        self.w_up = self.w_down = None
+
+    def tensors(self):
+        return {"up_proj.weight": TensorDecl((self.inter, self.hidden)),
+                "down_proj.weight": TensorDecl((self.hidden, self.inter))}
+
+    def bind(self, tensors):
+        self.w_up, self.w_down = tensors["up_proj.weight"], tensors["down_proj.weight"]
+
+    def forward(self, x, ctx) -> Branch:
+        z = linear(ctx, x, self.w_up, "ffn.up", torch.float32)
+        act = ctx.buffer("ffn.act", (x.shape[0], self.inter))
+        ctx.ops.act_rows(z, act, self.activation)
+        return Branch(linear(ctx, act, self.w_down, "ffn.out", torch.float32))
+
+
 register_part("ffn", "swiglu", SwiGLU)
+register_part("ffn", "dense_mlp", DenseMLP)

@@ -27,6 +27,12 @@ from .engine.engine import Engine
 from .weights.loader import load_model
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+_SPARE_REQUESTS = 256     # pages beyond --max-tokens, one per request that may be alive (see main)
+
+
+def _longest(model, tokens: int) -> int:
+    limit = model.spec.max_positions
+    return tokens if limit is None else min(limit, tokens)
 
 
 def main(argv=None) -> int:
@@ -45,9 +51,14 @@ def main(argv=None) -> int:
 
     print(f"[trace_run] loading {args.model} as {args.dtype}", file=sys.stderr, flush=True)
     model = load_model(args.model, dtype=_DTYPES[args.dtype], device=args.device)
+    # --max-tokens counts tokens, the cache hands out whole pages: every live request may leave most of its last
+    # page unused, so there is one page more for each of as many requests as could be alive at once
     pages = (args.max_tokens + 63) // 64
+    spare = min(pages, _SPARE_REQUESTS)
     # the longest single request: what the cache holds, or the model's position limit where that is less
-    engine = Engine(model, max_tokens=pages * 64, use_graphs=not args.no_graphs)
+    engine = Engine(model, max_tokens=(pages + spare) * 64, max_seq_len=_longest(model, pages * 64),
+                    n_slots=max(1, min(pages, 1024)), use_graphs=not args.no_graphs)
+    pages += spare
     print(f"[trace_run] ready: cache of {pages} pages of 64 tokens ({engine.cache.bytes() / 2**20:.1f} MiB)",
           file=sys.stderr, flush=True)
 

@@ -140,9 +140,14 @@ def random_tensors(decls, seed: int, *, std: float = 0.02, norm_std: float = 0.0
         ops = _ops_for(device)
     out = {}
     for name, d in decls.items():
-        mean, spread = (1.0, norm_std) if d.role == "norm" else (0.0, bias_std) if d.role == "bias" else (0.0, std)
+        # norm weights and the gains of residual streams scatter around 1, a stream-mixing matrix around the identity
+        near_one = d.role in ("norm", "stream_gain")
+        mean, spread = (1.0, norm_std) if near_one else (0.0, bias_std) if d.role == "bias" else \
+            (0.0, norm_std) if d.role == "stream_mix" else (0.0, std)
         t = torch.empty(d.shape, dtype=dtype, device=device)
         fill_normal(t, tensor_key(seed, name), mean, spread, ops)
+        if d.role == "stream_mix":
+            t += torch.eye(d.shape[0], dtype=dtype, device=device)
         out[name] = t
     return out
 

@@ -115,6 +115,72 @@ def silu_mul(gate_up, out):
     out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
 
 
+def hc_max_streams():
+    return 8
+
+
+def hc_add_rmsnorm(streams, branch, mix, write, read, weight, eps, out, rows=None):
+    idx = slice(None) if rows is None else rows.long()
+    x = streams[:, idx]
+    if branch is not None:
+        y = branch.sum(0)[idx]
+        x = torch.einsum("st,snd->tnd", mix, x) + write[:, None, None] * y[None]
+        streams[:, idx] = x
+    u = x.sum(0) if read is None else torch.einsum("s,snd->nd", read, x)
+    out.copy_((u * torch.rsqrt((u * u).mean(-1, keepdim=True) + eps) * weight.float()).to(out.dtype))
+
+
+def qkv_row_prep(qkvg, *, n_heads, n_kv_heads, head_dim, value_dim, bias, q_norm_w, k_norm_w, norm_eps, positions,
+                 q_out, gate_out=None, k_new=None, v_new=None, k_pages=None, v_pages=None, page_table=None,
+                 ring_pages=0, seq_of_token=None, slots=None):
+    x = qkvg.float().sum(0)
+    n = x.shape[0]
+    qw, kw, vw = n_heads * head_dim, n_kv_heads * head_dim, n_kv_heads * value_dim
+    if bias is not None:
+        x[:, :qw + kw + vw] += bias.float()
+    q, k, v = x[:, :qw], x[:, qw:qw + kw], x[:, qw + kw:qw + kw + vw]
+
+    def norm(t, w):
+        return t * torch.rsqrt((t * t).mean(-1, keepdim=True) + norm_eps) * w.float()
+
+    if q_norm_w is not None:
+        q = norm(q, q_norm_w)
+    if k_norm_w is not None:
+        k = norm(k, k_norm_w)
+    q_out.copy_(q.view(n, n_heads, head_dim).to(q_out.dtype))
+    if gate_out is not None:
+        gate_out.copy_(torch.sigmoid(x[:, qw + kw + vw:]))
+    k = k.reshape(n, n_kv_heads, head_dim).to(q_out.dtype)
+    v = v.reshape(n, n_kv_heads, value_dim).to(q_out.dtype)
+    if k_new is not None:
+        k_new.copy_(k)
+        v_new.copy_(v)
+    if k_pages is not None:
+        for t in range(n):
+            slot = int(slots[int(seq_of_token[t])])
+            pos = int(positions[t])
+            for h in range(n_kv_heads):
+                pg, hh, off = _rows_of(page_table, ring_pages, slot, pos, h, n_kv_heads)
+                k_pages[pg, hh, off] = k[t, h]
+                v_pages[pg, hh, off] = v[t, h]
+
+
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+
+
+def act_rows(x, out, kind):
+    z = x.float().sum(0)
+    if kind == "relu2":
+        y = torch.relu(z) ** 2
+    elif kind == "gelu_tanh":
+        y = torch.nn.functional.gelu(z, approximate="tanh")
+    elif kind == "silu":
+        y = z / (1 + torch.exp(-z))
+    else:
+        y = torch.relu(z)
+    out.copy_(y.to(out.dtype))
+
+
 def scatter_i32(dst, idx, val):
     dst.view(-1)[idx.long()] = val
 
@@ -127,10 +193,29 @@ def zero_rows(base, rows):
     base[rows.long()] = 0
 
 
-def _attend(q, keys, vals, scale):
+class AttentionForm:
+    def __init__(self, value_dim=0, sink=None, gated=False):
+        self.value_dim, self.sink, self.gated = int(value_dim), sink, bool(gated)
+
+    def plain(self, head_dim):
+        return self.value_dim in (0, head_dim) and self.sink is None and not self.gated
+
+    def vd(self, head_dim):
+        return self.value_dim or head_dim
+
+
+PLAIN_ATTENTION = AttentionForm()
+
+
+def _attend(q, keys, vals, scale, form=PLAIN_ATTENTION, gate=None):
     s = (keys.float() @ q.float()) * scale
-    p = torch.softmax(s, 0)
-    return p @ vals.float()
+    if form.sink is not None:
+        s = torch.cat([s, torch.tensor([float(form.sink)])])
+        p = torch.softmax(s, 0)[:-1]
+    else:
+        p = torch.softmax(s, 0)
+    o = p @ vals.float()
+    return o if gate is None else o * gate
 
 
 def _gather(k_pages, v_pages, page_table, ring_pages, slot, positions, kvh):
@@ -142,16 +227,16 @@ def _gather(k_pages, v_pages, page_table, ring_pages, slot, positions, kvh):
     return ks, vs
 
 
-def prefill_tile_queries(dtype, head_dim):
+def prefill_tile_queries(dtype, head_dim, form=PLAIN_ATTENTION):
     return 16
 
 
 def attn_prefill(q, k_new, v_new, k_pages, v_pages, page_table, ring_pages, tiles, cu_tokens, len_before,
-                 slots, out, *, scale, window, tile_queries=16):
+                 slots, out, *, scale, window, tile_queries=16, form=PLAIN_ATTENTION, gate=None):
     n, nh, hd = q.shape
     nkv = k_new.shape[1]
     g = nh // nkv
-    o = out.view(n, nh, hd)
+    o = out.view(n, nh, form.vd(hd))
     for b in range(slots.numel()):
         t0, t1 = int(cu_tokens[b]), int(cu_tokens[b + 1])
         lb = int(len_before[b])
@@ -166,30 +251,32 @@ def attn_prefill(q, k_new, v_new, k_pages, v_pages, page_table, ring_pages, tile
                 for p in range(max(lo, lb), pos + 1):
                     ks.append(k_new[t0 + p - lb, kvh])
                     vs.append(v_new[t0 + p - lb, kvh])
-                o[t, h] = _attend(q[t, h], torch.stack(ks), torch.stack(vs), scale).to(out.dtype)
+                o[t, h] = _attend(q[t, h], torch.stack(ks), torch.stack(vs), scale, form,
+                                  None if gate is None else gate[t, h]).to(out.dtype)
 
 
 class _Plan:
     scratch_floats, n_counters = 1, 0
 
 
-def attn_decode_plan(dtype, n_seqs, n_heads, n_kv_heads, head_dim, max_len):
+def attn_decode_plan(dtype, n_seqs, n_heads, n_kv_heads, head_dim, max_len, form=PLAIN_ATTENTION):
     return _Plan()
 
 
 def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, out, scratch, *,
-                scale, window, plan=None, n_splits=0, counters=None, balance=False):
+                scale, window, plan=None, n_splits=0, counters=None, balance=False, form=PLAIN_ATTENTION, gate=None):
     b_n, nh, hd = q.shape
     nkv = k_pages.shape[1]
     g = nh // nkv
-    o = out.view(b_n, nh, hd)
+    o = out.view(b_n, nh, form.vd(hd))
     for b in range(b_n):
         length = int(len_before[b]) + 1
         lo = max(0, length - window) if window > 0 else 0
         slot = int(slots[b])
         for h in range(nh):
             ks, vs = _gather(k_pages, v_pages, page_table, ring_pages, slot, range(lo, length), h // g)
-            o[b, h] = _attend(q[b, h], torch.stack(ks), torch.stack(vs), scale).to(out.dtype)
+            o[b, h] = _attend(q[b, h], torch.stack(ks), torch.stack(vs), scale, form,
+                              None if gate is None else gate[b, h]).to(out.dtype)
 
 
 def argmax(logits, out):
