@@ -355,7 +355,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         acc.w += w * v[k].w;
       }
     }
-    const float inv = L > 0.f ? 1.0f / L : 0.f;
+    if (a.has_sink) L += fast_exp2(a.sink_score * LOG2E - M);       // the sink's weight beside the keys'; it carries no value
+    float inv = L > 0.f ? 1.0f / L : 0.f;
+    if (a.gate) inv *= a.gate[pend_row];
     if (live) {
       uint2 packed;
       packed.x = pack_bf16(acc.x * inv, acc.y * inv);
@@ -530,7 +532,9 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
         const long long head_row = (long long)b * a.nh + kvh * G + head;
         if (whole) {
-          const float inv = L > 0.f ? 1.0f / L : 0.f;
+          if (a.has_sink) L += fast_exp2(a.sink_score * LOG2E - M);
+          float inv = L > 0.f ? 1.0f / L : 0.f;
+          if (a.gate) inv *= a.gate[head_row];
 #pragma unroll
           for (int dd = 0; dd < HD / 32; ++dd) out[head_row * HD + lane + 32 * dd] = __float2bfloat16_rn(acc[dd] * inv);
         } else {

@@ -295,7 +295,10 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_mma_kernel(PrefillArgs a)
   for (int r = 0; r < 2; ++r) {
     const int row = warp * 16 + g + r * 8;
     if (row >= nq) continue;
-    const float inv = l[r] > 0.f ? 1.0f / l[r] : 0.f;
+    float lr = l[r];
+    if (a.has_sink) lr += fast_exp2(a.sink_score * LOG2E - m[r]);   // the sink's weight beside the keys'; it carries no value
+    float inv = lr > 0.f ? 1.0f / lr : 0.f;
+    if (a.gate) inv *= a.gate[(long long)(tok0 + q_off + row) * a.nh + h];
     bf16* dst = out + ((long long)(tok0 + q_off + row) * a.nh + h) * hd;
 #pragma unroll
     for (int j = 0; j < HDMAX / 8; ++j) {
@@ -637,7 +640,9 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a, bf16
       if (ms != -INFINITY) L += expf(ms - M) * __ldcg(&a.part_ml[(base + s) * 2 + 1]);
     }
     L = warp_sum(L);
-    const float inv = L > 0.f ? 1.0f / L : 0.f;
+    if (a.has_sink) L += expf(a.sink_score - M);                    // M is in natural units here
+    float inv = L > 0.f ? 1.0f / L : 0.f;
+    if (a.gate) inv *= a.gate[(long long)b * a.nh + head];
     float oacc[HDMAX / 32];
 #pragma unroll
     for (int dd = 0; dd < HDMAX / 32; ++dd) oacc[dd] = 0.f;
@@ -694,6 +699,7 @@ LLG_API int llg_attn_prefill_mma(const PrefillArgs* args, cudaStream_t stream) {
               a.nh, a.nkv);
   LLG_REQUIRE(a.window >= 0 && a.ring_pages > 0 && a.table_width >= a.ring_pages, "attn_prefill_mma: bad cache geometry");
   LLG_REQUIRE(a.n_tiles <= 65535, "attn_prefill_mma: %d query tiles in one step are more than a grid takes (65535)", a.n_tiles);
+  LLG_REQUIRE(a.vd == 0 || a.vd == a.hd, "attn_prefill_mma: value heads of %d elements beside key heads of %d", a.vd, a.hd);
   if (a.n_tiles <= 0) return 0;
   const size_t smem = (size_t)4 * 64 * (a.hd * 2 + 16);
   dim3 grid(a.nh, a.n_tiles);
@@ -725,6 +731,7 @@ LLG_API int llg_attn_decode_mma(const DecodeArgs* args, void* out, int* counters
               resident / 2);
   LLG_REQUIRE(a.window >= 0 && a.ring_pages > 0 && a.table_width >= a.ring_pages, "attn_decode_mma: bad cache geometry");
   LLG_REQUIRE(counters != nullptr, "attn_decode_mma: needs n_seqs * nkv zeroed counters");
+  LLG_REQUIRE(a.vd == 0 || a.vd == a.hd, "attn_decode_mma: value heads of %d elements beside key heads of %d", a.vd, a.hd);
   if (a.n_seqs <= 0) return 0;
   size_t smem = (size_t)2 * DSTAGES * 64 * (a.hd * 2 + 16);
   const size_t merge = (size_t)4 * GH * (a.hd + 2) * sizeof(float);

@@ -572,7 +572,10 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(const __grid_co
     }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok && !*abortp) {
-      const float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+      // a sink joins the sum with its own weight 2^(sink - M) and carries no value; a gate scales the head's output
+      if (a.has_sink) l_run += fast_exp2(a.sink_score * LOG2E - m_run);
+      float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
+      if (a.gate && r < ti.nq[g]) inv *= a.gate[(long long)(q_tok0 + g * BQ + r) * a.nh + h];
       bf16* dst = (bf16*)a.out + ((long long)(q_tok0 + g * BQ + r) * a.nh + h) * HD;
 #pragma unroll
       for (int c0 = 0; c0 < HD; c0 += 16) {
@@ -697,6 +700,7 @@ LLG_API int llg_attn_prefill_tc(const PrefillArgs* args, cudaStream_t stream) {
   LLG_REQUIRE(a.window >= 0 && a.ring_pages > 0 && a.table_width >= a.ring_pages, "attn_prefill_tc: bad cache geometry");
   LLG_REQUIRE(a.n_tiles <= 65535, "attn_prefill_tc: %d query tiles in one step are more than a grid takes (65535)", a.n_tiles);
   LLG_REQUIRE(a.scale > 0.f, "attn_prefill_tc: the softmax scale must be positive");
+  LLG_REQUIRE(a.vd == 0 || a.vd == a.hd, "attn_prefill_tc: value heads of %d elements beside key heads of %d", a.vd, a.hd);
   LLG_REQUIRE(a.n_tokens > 0 && a.n_pages > 0, "attn_prefill_tc: needs the sizes of the packed rows and of the pages");
   LLG_REQUIRE(((uintptr_t)a.k_new % 16) == 0 && ((uintptr_t)a.v_new % 16) == 0 && ((uintptr_t)a.k_pages % 16) == 0 &&
                   ((uintptr_t)a.v_pages % 16) == 0,

@@ -124,6 +124,9 @@ struct DecodeTmaArgs {
   int n_seqs, nh, nkv, hd;
   float scale;
   int window;
+  int has_sink;               // as in PrefillArgs (value heads have the key heads' size here)
+  float sink_score;
+  const float* gate;          // [n_seqs][nh] or null
 };
 
 // Residual kept as several streams (hyper-connections), elementwise.cu: hc_add_rmsnorm.  For output row j (token

@@ -176,6 +176,7 @@ class _DecodeTmaArgs(Structure):
         ("q", c_void_p), ("page_table", c_void_p), ("table_width", c_int), ("ring_pages", c_int),
         ("slots", c_void_p), ("len_before", c_void_p), ("part", c_void_p), ("counters", c_void_p), ("out", c_void_p),
         ("n_seqs", c_int), ("nh", c_int), ("nkv", c_int), ("hd", c_int), ("scale", c_float), ("window", c_int),
+        ("has_sink", c_int), ("sink_score", c_float), ("gate", c_void_p),
     ]
 
 
@@ -670,6 +671,10 @@ class AttentionForm:
     def plain(self, head_dim: int) -> bool:
         return self.value_dim in (0, head_dim) and self.sink is None and not self.gated
 
+    def one_head_size(self, head_dim: int) -> bool:
+        """Keys and values of one head size: what the tensor-core kernels take (sink and gate they all apply)."""
+        return self.value_dim in (0, head_dim)
+
     def vd(self, head_dim: int) -> int:
         return self.value_dim or head_dim
 
@@ -678,8 +683,9 @@ PLAIN_ATTENTION = AttentionForm()
 
 
 def _prefill_kernel(dtype: torch.dtype, head_dim: int, form: AttentionForm) -> str:
-    """Which prompt attention kernel takes this geometry and form."""
-    if form.plain(head_dim):
+    """Which prompt attention kernel takes this geometry and form: the tensor-core kernels want keys and values
+    of one head size."""
+    if form.one_head_size(head_dim):
         return "tc" if _use_tc_attn(dtype, head_dim) else "mma" if _use_mma(dtype, head_dim) else "simt"
     return "simt"
 
@@ -790,9 +796,9 @@ def attn_decode_plan(dtype: torch.dtype, n_seqs: int, n_heads: int, n_kv_heads: 
 
     bfloat16 at head sizes 64 / 128: the TMA kernel, which balances the work itself from the lengths it finds on
     the device.  Other multiples of 16 up to 128: the mma.sync kernel with a split count from ``max_len`` (per
-    sequence by its length for small batches).  Everything else, and every form but the plain one: the CUDA-core
-    kernel."""
-    plain = form.plain(head_dim)
+    sequence by its length for small batches).  Everything else, and values of another head size than the keys: the
+    CUDA-core kernel."""
+    plain = form.one_head_size(head_dim)
     if plain and _use_tma_decode(dtype, head_dim, n_heads, n_kv_heads, n_seqs):
         lib = _lib("attention_decode_tma")
         floats = lib.llg_attn_decode_tma_scratch_floats(n_seqs, n_heads, n_kv_heads, head_dim, max_len)
@@ -855,8 +861,8 @@ def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, 
         raise KernelError("attn_decode: the scratch must be float32")
     if form.gated != (gate is not None) or (gate is not None and tuple(gate.shape) != (b, nh)):
         raise KernelError("attn_decode: a gated form needs a gate [sequences, heads], and only a gated form takes one")
-    if not form.plain(hd) and plan is not None and plan.kind != "simt":
-        raise KernelError(f"attn_decode: the {plan.kind} kernel computes the plain form only")
+    if not form.one_head_size(hd) and plan is not None and plan.kind != "simt":
+        raise KernelError(f"attn_decode: the {plan.kind} kernel takes keys and values of one head size")
     assert out.shape == (b, nh * vd) and v_pages.shape[3] == vd
     if plan is not None and plan.kind == "tma":
         lib = _lib("attention_decode_tma")
@@ -871,12 +877,14 @@ def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, 
         a.part, a.counters, a.out = _ptr(scratch), _ptr(counters, torch.int32), _ptr(out, torch.bfloat16)
         a.n_seqs, a.nh, a.nkv, a.hd = b, nh, nkv, hd
         a.scale, a.window = float(scale), int(window)
+        a.has_sink, a.sink_score = (0, 0.0) if form.sink is None else (1, form.sink)
+        a.gate = _ptr(gate, torch.float32)
         _check(lib, lib.llg_attn_decode_tma(byref(a), _ptr(k_pages, torch.bfloat16), _ptr(v_pages, torch.bfloat16),
                                             k_pages.shape[0], int(plan.max_len), _stream()))
         return
     if plan is not None:
         n_splits, balance = plan.n_splits, plan.balance
-    mma = form.plain(hd) and _use_mma(q.dtype, hd)
+    mma = form.one_head_size(hd) and _use_mma(q.dtype, hd)
     lib = _lib("attention_mma" if mma else "attention_simt")
     need = b * nh * n_splits * (vd + 2)
     if n_splits < 1 or scratch.numel() < need:

@@ -64,49 +64,37 @@ class ModelCosts:
 
 
 def model_costs(model) -> ModelCosts:
-    """Read off a built model: matrices by their declarations, cache bytes by what the mixers keep."""
+    """Read off a built model: matrices by the declarations of the parts that the run order passes through (a layer
+    named twice runs twice), cache bytes by what the mixers keep."""
     import torch
     from .parts.base import KvNeed
     elem = 2 if model.dtype == torch.bfloat16 else 4
-    head = 0
-    matrix = 0
-    decls = model.tensor_decls()
-    head_prefix = model.head.prefix
-    for name, d in decls.items():
-        if d.role != "matrix":
-            continue
-        n = 1
-        for s in d.shape:
-            n *= int(s)
-        if name.startswith(head_prefix):
-            head += n
-        else:
-            matrix += n
+
+    def matrices(part) -> int:
+        total = 0
+        for d in part.tensors().values():
+            if d.role == "matrix":
+                n = 1
+                for s in d.shape:
+                    n *= int(s)
+                total += n
+        return total
+
+    head = matrices(model.head)
     if head == 0:                                        # tied: the embedding table serves as the output matrix
         head = int(model.spec.vocab_size) * int(model.spec.hidden_size)
-    # a layer that the run order names twice runs twice
-    per_layer = {}
-    for name, d in decls.items():
-        if d.role == "matrix" and name.startswith("model.layers."):
-            idx = int(name.split(".")[2])
-            n = 1
-            for s in d.shape:
-                n *= int(s)
-            per_layer[idx] = per_layer.get(idx, 0) + n
-    if per_layer:
-        counted = sum(per_layer.values())
-        scheduled = sum(per_layer.get(e.layer, 0) for e in model.spec.schedule)
-        matrix += scheduled - counted
+    matrix = 0
     kv, attn = [], 0
-    for e_i, e in enumerate(model.spec.schedule):
+    for e in model.spec.schedule:
         block = model.blocks[e.layer]
+        matrix += sum(matrices(part) for part in block.parts.values())
         need = block.cache_need()
-        if isinstance(need, KvNeed):
-            kv.append((2 * need.num_kv_heads * need.head_dim * elem, need.window))
+        if isinstance(need, KvNeed) and e.cache_of is None:
+            kv.append((need.num_kv_heads * (need.head_dim + (need.value_dim or need.head_dim)) * elem, need.window))
         for part in block.parts.values():
             nh, hd = getattr(part, "nh", None), getattr(part, "hd", None)
             if nh and hd:
-                attn += 4 * nh * hd
+                attn += 2 * nh * (hd + (getattr(part, "vd", None) or hd))
     return ModelCosts(matrix, head, elem, tuple(kv), attn)
 
 
