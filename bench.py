@@ -19,6 +19,9 @@ tokens, 256 steps) and ``qwen25_14b_b32_128steps`` (32 prompts of 256 to 8,192 t
 decoded tokens per second over the whole run and the mean fraction of the copy bandwidth that the bytes of its decode
 steps stand for.  The two workloads of a few hundred steps are run twice and the second run is the one reported (the first
 records the CUDA graphs of its decode steps inside its decode time); the one of thousands of steps is run once.  ``--no-workloads`` leaves them out.
+
+``--probe designs`` prints another line instead: the Karitar design beside the closest stock model (Qwen3) at equal layer
+sizes (``--sizes``), prompt and decode throughput of each and every kernel of the two steps against its roofline.
 """
 import argparse
 import json
@@ -354,6 +357,179 @@ def probe_timeline(torch, L, ops, cfg, batch, context, prompt_tokens=0):
     return 0
 
 
+# ---- two designs side by side -----------------------------------------------------------------
+
+# Layer sizes that resemble real models' (a few layers each, random weights): name -> (width, heads, key/value heads,
+# head size, feed-forward size, window or None, context of the decode steps)
+DESIGN_SIZES = {"1b-like": (2048, 32, 8, 64, 8192, 1024, 4096), "8b-like": (4096, 32, 8, 128, 14336, None, 8192)}
+DESIGN_LAYERS, DESIGN_VOCAB = 4, 32000
+
+
+def design_configs(size):
+    """The Karitar configuration of a size and the closest stock model's (Qwen3: grouped-query attention with normed
+    queries and keys and the same window, pre-norm blocks) with the same width, heads, head size and feed-forward size."""
+    width, heads, kv, hd, ff, window, _ = DESIGN_SIZES[size]
+    mixer = {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5}
+    if window:
+        mixer["mask"] = {"size": window}
+    karitar = {"architecture": "Karitar", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-5}, "streams": 2,
+               "layers": [{"type": "attention", "mixer": dict(mixer), "mlp": {"kind": "dense", "ff": ff}}
+                          for _ in range(DESIGN_LAYERS)]}
+    qwen3 = {"architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": DESIGN_LAYERS, "hidden_size": width,
+             "num_attention_heads": heads, "num_key_value_heads": kv, "head_dim": hd, "intermediate_size": ff,
+             "vocab_size": DESIGN_VOCAB, "rope_theta": 1000000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False}
+    if window:
+        qwen3.update(sliding_window=window, layer_types=["sliding_attention"] * DESIGN_LAYERS)
+    return {"karitar": karitar, "qwen3": qwen3}
+
+
+_TIMED_OPS = ("embed_rows", "add_rmsnorm", "hc_add_rmsnorm", "qk_prep", "qkv_row_prep", "gemm_tc", "gemm_tc_act", "gemm_tc_qkv",
+              "act_rows", "silu_mul", "attn_prefill", "attn_decode", "kv_write")
+
+
+def _kernel_label(name, args, kw):
+    """A row of the per-kernel table: products are told apart by what they feed."""
+    if name in ("gemm_tc", "gemm_tc_act", "gemm_tc_qkv"):
+        o, k = args[1].shape
+        what = "gated" if kw.get("gated_features") else "act" if name == "gemm_tc_act" else "qkv+prep" if name == "gemm_tc_qkv" else ""
+        return f"product {k}->{o} {what}".strip()
+    return name
+
+
+def _kernel_cost(name, args, kw, keys_read):
+    """(bytes that must move, flops) of one call, from its tensor arguments; attention from the keys it reads."""
+    import torch as _t
+    tensors = [a for a in list(args) + list(kw.values()) if isinstance(a, _t.Tensor)]
+    if name in ("gemm_tc", "gemm_tc_act", "gemm_tc_qkv"):
+        x, w = args[0], args[1]
+        out = args[2] if len(args) > 2 and isinstance(args[2], _t.Tensor) else kw.get("q_out")
+        return x.nbytes + w.nbytes + (out.nbytes if out is not None else 0), 2.0 * x.shape[0] * w.shape[0] * w.shape[1]
+    if name in ("attn_prefill", "attn_decode"):
+        q = args[0]
+        n, nh, hd = q.shape
+        kp, vp = (args[3], args[4]) if name == "attn_prefill" else (args[1], args[2])
+        nkv, vd = kp.shape[1], vp.shape[3]
+        pairs, rows = keys_read
+        return rows * nkv * (hd + vd) * q.element_size() + 2 * q.nbytes, 2.0 * nh * (hd + vd) * pairs
+    if name in ("qk_prep", "qkv_row_prep", "kv_write"):
+        # the page stores are arguments, but only the step's rows of them are written
+        moved = sum(t.nbytes for t in tensors if t.dim() != 4)
+        return moved, 0.0
+    return sum(t.nbytes for t in tensors), 0.0
+
+
+def probe_designs(torch, L, ops, pk, sizes, batch):
+    """Prefill and decode throughput of Karitar beside the closest stock model at equal layer sizes, and every kernel of
+    the two steps against its roofline (the slower of bytes / copy bandwidth and flops / matrix peak)."""
+    os.environ["LLOGOS_RUNNER"] = "0"           # the parts call the kernels one by one, so each call can be timed
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    gen = torch.Generator().manual_seed(1)
+    report = {}
+    real = {n: getattr(ops, n) for n in _TIMED_OPS}
+    for size in sizes:
+        window, context = DESIGN_SIZES[size][5], DESIGN_SIZES[size][6]
+        for design, cfg in design_configs(size).items():
+            model = L.weights.random_model(cfg, seed=0, dtype=torch.bfloat16, device=dev, std=0.02)
+            out = {}
+            for graphs in (True, False):
+                eng = L.engine.Engine(model, max_tokens=(batch + 1) * pages_of(context), max_seq_len=context, n_slots=batch + 1,
+                                      use_graphs=graphs)
+                for g in eng.cache.kv_groups:
+                    for t in list(g.k.values()) + list(g.v.values()):
+                        t.normal_(0.0, 1.0)
+                toks = torch.randint(0, DESIGN_VOCAB, (PREFILL_TOKENS,), generator=gen).tolist()
+                steps, warmup = 24, 4
+                dtok = torch.randint(0, DESIGN_VOCAB, (steps + warmup, batch), generator=gen).tolist()
+                records = []
+                # Timing kernel by kernel: the host needs longer to issue a launch than most kernels run, and an event
+                # pair around a launch would then measure the host.  So the device is first kept busy by a spin kernel
+                # for about as long as the host needs to queue the whole step; the step's kernels then run back to back.
+                hold = (lambda: None) if graphs else (lambda: torch.cuda._sleep(int(4e7)))
+                if not graphs:
+                    def timed(name):
+                        def f(*a, **kw):
+                            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                            e0.record()
+                            real[name](*a, **kw)
+                            e1.record()
+                            records.append((phase[0], name, a, kw, e0, e1))
+                        return f
+                    for n in _TIMED_OPS:
+                        setattr(ops, n, timed(n))
+                phase = ["warm"]
+                # prompt step of 2,048 tokens
+                times = []
+                for it in range(3 + 3):
+                    phase[0] = "prefill" if it >= 3 else "warm"
+                    slot = eng.open()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    torch.cuda.synchronize()
+                    hold()
+                    e0.record()
+                    eng.step([(slot, toks)])
+                    e1.record()
+                    torch.cuda.synchronize()
+                    if it >= 3:
+                        times.append(e0.elapsed_time(e1))
+                    eng.close(slot)
+                pre_ms = sorted(times)[len(times) // 2]
+                # decode steps at the context length
+                phase[0] = "warm"
+                slots = [eng.open() for _ in range(batch)]
+                for sl in slots:
+                    eng.assume(sl, context - (steps + warmup))
+                for i in range(warmup):
+                    eng.step([(sl, [dtok[i][j]]) for j, sl in enumerate(slots)])
+                phase[0] = "decode"
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                torch.cuda.synchronize()
+                e0.record()
+                for i in range(warmup, warmup + steps):
+                    hold()
+                    eng.step([(sl, [dtok[i][j]]) for j, sl in enumerate(slots)])
+                e1.record()
+                torch.cuda.synchronize()
+                dec_ms = e0.elapsed_time(e1) / steps
+                for n in _TIMED_OPS:
+                    setattr(ops, n, real[n])
+                if graphs:
+                    out.update(prefill_tokens=PREFILL_TOKENS, prefill_ms=round(pre_ms, 3),
+                               prefill_tokens_per_s=round(PREFILL_TOKENS / pre_ms * 1e3, 1), decode_batch=batch,
+                               decode_context=context, decode_ms_per_step=round(dec_ms, 4),
+                               decode_tokens_per_s=round(batch / dec_ms * 1e3, 1))
+                else:
+                    keys = min(window, context) if window else context
+                    t = PREFILL_TOKENS
+                    pre_pairs = sum(min(i + 1, window) if window else i + 1 for i in range(t))
+                    table = {}
+                    for ph, name, a, kw, ev0, ev1 in records:
+                        if ph == "warm":
+                            continue
+                        kr = (pre_pairs, t) if ph == "prefill" else (batch * keys, batch * keys)
+                        nbytes, flops = _kernel_cost(name, a, kw, kr)
+                        row = table.setdefault((ph, _kernel_label(name, a, kw)), [0, 0.0, 0.0, 0.0])
+                        row[0] += 1
+                        row[1] += ev0.elapsed_time(ev1) * 1e3
+                        row[2] += nbytes
+                        row[3] += flops
+                    rows = []
+                    for (ph, label), (calls, us, nbytes, flops) in sorted(table.items()):
+                        floor_us = max(nbytes / (pk["hbm_gbs"] * 1e3), flops / (pk["bf16_tflops"] * 1e6))
+                        rows.append({"step": ph, "kernel": label, "calls": calls, "us_per_call": round(us / calls, 2),
+                                     "roofline_us": round(floor_us / calls, 2), "fraction_of_roofline": round(floor_us / us, 3)})
+                    out["kernels"] = rows
+                del eng
+                torch.cuda.empty_cache()
+            report.setdefault(size, {})[design] = out
+            print(f"[bench] {size} {design}: " + json.dumps({k: v for k, v in out.items() if k != "kernels"}), file=sys.stderr, flush=True)
+            del model
+            torch.cuda.empty_cache()
+    print(json.dumps({"probe": "designs", "peaks": pk, "layers": DESIGN_LAYERS, "vocab": DESIGN_VOCAB, "dtype": "bf16",
+                      "data": "synthetic (random weights, random tokens)", "sizes": report}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -370,10 +546,13 @@ def main():
     ap.add_argument("--no-workloads", action="store_true", help="leave out the workloads of the other shapes and the ragged run")
     ap.add_argument("--tokens", type=int, default=0,
                     help="with --probe timeline: the time line of a prompt step of so many tokens instead of a decode step")
-    ap.add_argument("--probe", choices=["decode-attention", "leave-one-out", "timeline"],
+    ap.add_argument("--sizes", default=",".join(DESIGN_SIZES), help="with --probe designs: which of " + ", ".join(DESIGN_SIZES))
+    ap.add_argument("--probe", choices=["decode-attention", "leave-one-out", "timeline", "designs"],
                     help="instead of the bench line, print a table: decode attention alone over batch shapes; what "
                          "the decode step loses when each kernel in turn is left out of the recorded graph; or one "
-                         "decode step's launches on a time line (needs LLOGOS_NVCC_FLAGS=-DLLG_STAMPS; --layers, default 6)")
+                         "decode step's launches on a time line (needs LLOGOS_NVCC_FLAGS=-DLLG_STAMPS; --layers, default 6); "
+                         "or the Karitar design beside the closest stock model at equal layer sizes (throughput of prompt and "
+                         "decode steps, and every kernel against its roofline)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -396,6 +575,8 @@ def main():
         return probe_decode_attention(torch, ops, SHAPES[args.shape][1], pk)
     if args.probe == "leave-one-out":
         return probe_leave_one_out(torch, L, ops, dict(SHAPES[args.shape][1]), args.batch, args.context)
+    if args.probe == "designs":
+        return probe_designs(torch, L, ops, pk, [s for s in args.sizes.split(",") if s in DESIGN_SIZES], args.batch)
     if args.probe == "timeline":
         return probe_timeline(torch, L, ops, dict(SHAPES[args.shape][1], num_hidden_layers=args.layers or 6),
                               args.batch, args.context, args.tokens)

@@ -140,6 +140,18 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
   return __float2bfloat16_rn(v);
 }
 
+// ---- activations of an ungated feed-forward --------------------------------------------
+// Kinds: 0 relu(z)^2, 1 gelu in its tanh form 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), 2 silu, 3 relu.
+#define LLG_ACT_KINDS 4
+__device__ __forceinline__ float llg_act(int kind, float z) {
+  switch (kind) {
+    case 0: { const float r = fmaxf(z, 0.f); return r * r; }
+    case 1: return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    case 2: return z / (1.0f + expf(-z));
+    default: return fmaxf(z, 0.f);
+  }
+}
+
 // ---- reductions -------------------------------------------------------------------
 
 __device__ __forceinline__ float warp_sum(float v) {

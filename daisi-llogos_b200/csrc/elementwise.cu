@@ -773,6 +773,104 @@ __global__ void hc_add_rmsnorm_kernel(HyperNormArgs a) {
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = from_f32<OT>(u_row[i] * inv * to_f32(w[i]));
 }
 
+// The same for rows whose length is a multiple of 4 and 16-byte aligned operands: 16-byte accesses, the read-out stays in
+// registers between the two passes (VPT float4 per thread), and the partial sums of an element are asked for together.
+// SMAX: the most streams an instance holds (its register arrays have that size).
+template <typename OT, typename WT, int VPT, int SMAX>
+__global__ void __launch_bounds__(512) hc_add_rmsnorm_vec4_kernel(HyperNormArgs a) {
+  pdl_launch_dependents();
+  __shared__ float red[32];
+  __shared__ float c_mix[HC_MAX * HC_MAX], c_write[HC_MAX], c_read[HC_MAX];
+  const int S = a.n_streams;
+  const int nv = a.hidden >> 2;
+  if (threadIdx.x < S * S) c_mix[threadIdx.x] = a.branch ? a.mix[threadIdx.x] : 0.f;
+  if (threadIdx.x < S) {
+    c_write[threadIdx.x] = a.branch ? a.write[threadIdx.x] : 0.f;
+    c_read[threadIdx.x] = a.read ? a.read[threadIdx.x] : 1.f;
+  }
+  float wv[VPT][4];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < nv) vec_load4((const WT*)a.weight + 4 * i, wv[k]);
+  }
+  pdl_wait();
+  __syncthreads();
+  const int j = blockIdx.x;
+  const int r = a.rows ? a.rows[j] : j;
+  float4* base = reinterpret_cast<float4*>(a.streams + (long long)r * a.hidden);
+  const long long ss4 = a.stream_stride >> 2, ps4 = a.partial_stride >> 2;
+  float4 keep[VPT];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < nv) {
+      float4 x[SMAX];
+#pragma unroll
+      for (int s = 0; s < SMAX; ++s) x[s] = s < S ? base[s * ss4 + i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      if (a.branch) {
+        const float4* b = reinterpret_cast<const float4*>(a.branch + (long long)r * a.hidden) + i;
+        float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+        int p = 0;
+        for (; p + 4 <= a.n_partials; p += 4) {
+          const float4 b0 = b[(p + 0) * ps4], b1 = b[(p + 1) * ps4], b2 = b[(p + 2) * ps4], b3 = b[(p + 3) * ps4];
+          y.x += b0.x; y.y += b0.y; y.z += b0.z; y.w += b0.w;
+          y.x += b1.x; y.y += b1.y; y.z += b1.z; y.w += b1.w;
+          y.x += b2.x; y.y += b2.y; y.z += b2.z; y.w += b2.w;
+          y.x += b3.x; y.y += b3.y; y.z += b3.z; y.w += b3.w;
+        }
+        for (; p < a.n_partials; ++p) {
+          const float4 b0 = b[p * ps4];
+          y.x += b0.x; y.y += b0.y; y.z += b0.z; y.w += b0.w;
+        }
+        float4 nx[SMAX];
+#pragma unroll
+        for (int t = 0; t < SMAX; ++t) {
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (t < S) {
+#pragma unroll
+            for (int s = 0; s < SMAX; ++s) {
+              if (s < S) {
+                const float m = c_mix[s * S + t];
+                v.x = fmaf(m, x[s].x, v.x); v.y = fmaf(m, x[s].y, v.y); v.z = fmaf(m, x[s].z, v.z); v.w = fmaf(m, x[s].w, v.w);
+              }
+            }
+            const float wr = c_write[t];
+            v.x = fmaf(wr, y.x, v.x); v.y = fmaf(wr, y.y, v.y); v.z = fmaf(wr, y.z, v.z); v.w = fmaf(wr, y.w, v.w);
+            base[t * ss4 + i] = v;
+          }
+          nx[t] = v;
+        }
+#pragma unroll
+        for (int t = 0; t < SMAX; ++t) x[t] = nx[t];
+      }
+#pragma unroll
+      for (int s = 0; s < SMAX; ++s) {
+        if (s < S) {
+          const float rd = c_read[s];
+          u.x = fmaf(rd, x[s].x, u.x); u.y = fmaf(rd, x[s].y, u.y); u.z = fmaf(rd, x[s].z, u.z); u.w = fmaf(rd, x[s].w, u.w);
+        }
+      }
+    }
+    keep[k] = u;
+    ss += u.x * u.x + u.y * u.y + u.z * u.z + u.w * u.w;
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)a.hidden + a.eps);
+  OT* o = (OT*)a.out + (long long)j * a.hidden;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < nv) {
+      const float4 u = keep[k];
+      const float y[4] = {u.x * inv * wv[k][0], u.y * inv * wv[k][1], u.z * inv * wv[k][2], u.w * inv * wv[k][3]};
+      vec_store4(o + 4 * i, y);
+    }
+  }
+}
+
 LLG_API int llg_hc_max_streams() { return HC_MAX; }
 
 LLG_API int llg_hc_add_rmsnorm(const HyperNormArgs* args, cudaStream_t stream) {
@@ -784,9 +882,37 @@ LLG_API int llg_hc_add_rmsnorm(const HyperNormArgs* args, cudaStream_t stream) {
   if (a.n_out == 0) return 0;
   const size_t smem = (size_t)a.hidden * sizeof(float);
   LLG_REQUIRE(smem <= 200 * 1024, "hc_add_rmsnorm: rows of %d elements do not fit shared memory", a.hidden);
-  const int threads = a.hidden >= 2048 ? 512 : (a.hidden >= 512 ? 256 : 128);
+  int threads = a.hidden >= 2048 ? 512 : (a.hidden >= 512 ? 256 : 128);
+  // vector path (as in llg_add_rmsnorm): few rows want many threads per row, many rows want the row in registers
+  auto aligned = [](const void* p) { return ((uintptr_t)p & 15u) == 0; };
+  const bool vec = a.hidden % 4 == 0 && a.stream_stride % 4 == 0 && a.partial_stride % 4 == 0 && aligned(a.streams) &&
+                   aligned(a.branch) && aligned(a.weight) && aligned(a.out);
+  int vpt = 1;
+  if (vec) {
+    const int nv = a.hidden / 4;
+    // (at most 512 threads: a thread holds S float4 of the streams beside its part of the read-out)
+    threads = a.n_out <= 256 ? (nv >= 512 ? 512 : (nv >= 256 ? 256 : 128)) : (nv >= 1024 ? 512 : 256);
+    vpt = (nv + threads - 1) / threads;
+    if (vpt > 4) {
+      threads = 512;
+      vpt = (nv + threads - 1) / threads;
+    }
+  }
+  const bool vec_ok = vec && vpt <= 4;
+#define LAUNCH_V(OT, WT, SM)                                                                                        \
+  do {                                                                                                              \
+    if (vpt <= 1) llg_launch(hc_add_rmsnorm_vec4_kernel<OT, WT, 1, SM>, a.n_out, threads, 0, stream, a);            \
+    else if (vpt <= 2) llg_launch(hc_add_rmsnorm_vec4_kernel<OT, WT, 2, SM>, a.n_out, threads, 0, stream, a);       \
+    else llg_launch(hc_add_rmsnorm_vec4_kernel<OT, WT, 4, SM>, a.n_out, threads, 0, stream, a);                     \
+  } while (0)
 #define LAUNCH(OT, WT)                                                                                              \
   do {                                                                                                              \
+    if (vec_ok) {                                                                                                   \
+      if (a.n_streams <= 2) LAUNCH_V(OT, WT, 2);                                                                    \
+      else if (a.n_streams <= 4) LAUNCH_V(OT, WT, 4);                                                               \
+      else LAUNCH_V(OT, WT, HC_MAX);                                                                                \
+      break;                                                                                                        \
+    }                                                                                                               \
     if (smem > 48 * 1024) {                                                                                         \
       cudaError_t e = cudaFuncSetAttribute(hc_add_rmsnorm_kernel<OT, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
       if (e != cudaSuccess) return llg_fail("hc_add_rmsnorm: shared memory %zu: %s", smem, cudaGetErrorString(e));   \
@@ -799,6 +925,7 @@ LLG_API int llg_hc_add_rmsnorm(const HyperNormArgs* args, cudaStream_t stream) {
   else if (a.out_dtype == LLG_BF16 && a.weight_dtype == LLG_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16);
   else return llg_fail("hc_add_rmsnorm: unknown dtypes out=%d weight=%d", a.out_dtype, a.weight_dtype);
 #undef LAUNCH
+#undef LAUNCH_V
   return llg_check_launch("hc_add_rmsnorm");
 }
 
@@ -861,6 +988,92 @@ __global__ void qkv_row_prep_kernel(QkvRowPrepArgs a) {
   }
 }
 
+// The same with 16-byte accesses, for head sizes and head counts that are multiples of 4 (every part of the row then
+// starts and ends on a group of four) and 16-byte aligned operands.
+__device__ __forceinline__ void vec_store4_any(float* p, const float (&v)[4]) { vec_store4(p, v); }
+__device__ __forceinline__ void vec_store4_any(__nv_bfloat16* p, const float (&v)[4]) { vec_store4(p, v); }
+
+template <typename OT, typename WT>
+__global__ void qkv_row_prep_vec4_kernel(QkvRowPrepArgs a) {
+  pdl_launch_dependents();
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  const int n = blockIdx.x;
+  const int Q = a.nh * a.hd, K = a.nkv * a.hd, V = a.nkv * a.vd, G = a.gate_out ? a.nh : 0;
+  const int W = Q + K + V + G, W4 = W >> 2;
+  const WT* bias = (const WT*)a.bias;
+  // positions, slots and the page table were written before this step's first kernel started
+  const int pos = a.positions[n];
+  const bool to_pages = a.k_pages != nullptr;
+  const int slot = to_pages ? a.slots[a.seq_of_token[n]] : 0;
+  pdl_wait();
+  const float4* src = reinterpret_cast<const float4*>(a.qkvg + (long long)n * W);
+  const long long ps4 = a.partial_stride >> 2;
+  float ss_q = 0.f, ss_k = 0.f;
+  for (int i4 = threadIdx.x; i4 < W4; i4 += blockDim.x) {
+    const int i = i4 << 2;
+    float4 v = src[i4];
+    for (int p = 1; p < a.n_partials; ++p) {
+      const float4 t = src[p * ps4 + i4];
+      v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+    }
+    if (bias && i < Q + K + V) {
+      float b[4];
+      vec_load4(bias + i, b);
+      v.x += b[0]; v.y += b[1]; v.z += b[2]; v.w += b[3];
+    }
+    reinterpret_cast<float4*>(row)[i4] = v;
+    const float sq = v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+    if (i < Q) ss_q += sq;
+    else if (i < Q + K) ss_k += sq;
+  }
+  ss_q = block_sum(ss_q, red);
+  ss_k = block_sum(ss_k, red);
+  __syncthreads();
+  const float inv_q = a.q_norm_w ? 1.0f / sqrtf(ss_q / (float)Q + a.norm_eps) : 1.f;
+  const float inv_k = (a.k_norm_w && K > 0) ? 1.0f / sqrtf(ss_k / (float)K + a.norm_eps) : 1.f;
+  const WT* qw = (const WT*)a.q_norm_w;
+  const WT* kw = (const WT*)a.k_norm_w;
+  for (int i4 = threadIdx.x; i4 < W4; i4 += blockDim.x) {
+    const int i = i4 << 2;
+    const float4 t = reinterpret_cast<const float4*>(row)[i4];
+    float v[4] = {t.x, t.y, t.z, t.w};
+    if (i < Q) {
+      if (qw) {
+        float w[4];
+        vec_load4(qw + i, w);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) v[c] = v[c] * inv_q * w[c];
+      }
+      vec_store4_any((OT*)a.q_out + (long long)n * Q + i, v);
+    } else if (i < Q + K) {
+      const int c0 = i - Q;
+      if (kw) {
+        float w[4];
+        vec_load4(kw + c0, w);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) v[c] = v[c] * inv_k * w[c];
+      }
+      if (a.k_new) vec_store4_any((OT*)a.k_new + (long long)n * K + c0, v);
+      if (to_pages) {
+        const long long r = kv_row(a.page_table, a.table_width, a.ring_pages, slot, pos, c0 / a.hd, a.nkv);
+        vec_store4_any((OT*)a.k_pages + r * a.hd + c0 % a.hd, v);
+      }
+    } else if (i < Q + K + V) {
+      const int c0 = i - Q - K;
+      if (a.v_new) vec_store4_any((OT*)a.v_new + (long long)n * V + c0, v);
+      if (to_pages) {
+        const long long r = kv_row(a.page_table, a.table_width, a.ring_pages, slot, pos, c0 / a.vd, a.nkv);
+        vec_store4_any((OT*)a.v_pages + r * a.vd + c0 % a.vd, v);
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) v[c] = 1.0f / (1.0f + expf(-v[c]));
+      vec_store4(a.gate_out + (long long)n * a.nh + (i - Q - K - V), v);
+    }
+  }
+}
+
 LLG_API int llg_qkv_row_prep(const QkvRowPrepArgs* args, int out_dtype, cudaStream_t stream) {
   const QkvRowPrepArgs& a = *args;
   LLG_REQUIRE(a.n_tokens >= 0 && a.nh > 0 && a.nkv >= 0 && a.hd > 0 && a.vd > 0, "qkv_row_prep: bad sizes");
@@ -872,14 +1085,21 @@ LLG_API int llg_qkv_row_prep(const QkvRowPrepArgs* args, int out_dtype, cudaStre
   const long long w = (long long)a.nh * a.hd + (long long)a.nkv * (a.hd + a.vd) + (a.gate_out ? a.nh : 0);
   const size_t smem = (size_t)w * sizeof(float);
   LLG_REQUIRE(smem <= 200 * 1024, "qkv_row_prep: rows of %lld elements do not fit shared memory", w);
-  const int threads = w >= 2048 ? 512 : 256;
+  auto aligned = [](const void* p) { return ((uintptr_t)p & 15u) == 0; };
+  const bool vec = a.hd % 4 == 0 && a.vd % 4 == 0 && a.nh % 4 == 0 && a.partial_stride % 4 == 0 && aligned(a.qkvg) &&
+                   aligned(a.bias) && aligned(a.q_norm_w) && aligned(a.k_norm_w) && aligned(a.q_out) && aligned(a.k_new) &&
+                   aligned(a.v_new) && aligned(a.k_pages) && aligned(a.v_pages) && aligned(a.gate_out);
+  // few tokens: the row's loads are the step's critical path, so more threads share them
+  const int threads = vec ? (w >= 4096 && a.n_tokens <= 64 ? 1024 : (w >= 2048 && a.n_tokens <= 256) ? 512 : 256) : (w >= 2048 ? 512 : 256);
 #define LAUNCH(OT, WT)                                                                                             \
   do {                                                                                                             \
     if (smem > 48 * 1024) {                                                                                        \
       cudaError_t e = cudaFuncSetAttribute(qkv_row_prep_kernel<OT, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e == cudaSuccess) e = cudaFuncSetAttribute(qkv_row_prep_vec4_kernel<OT, WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
       if (e != cudaSuccess) return llg_fail("qkv_row_prep: shared memory %zu: %s", smem, cudaGetErrorString(e));    \
     }                                                                                                              \
-    llg_launch(qkv_row_prep_kernel<OT, WT>, a.n_tokens, threads, smem, stream, a);                                 \
+    if (vec) llg_launch(qkv_row_prep_vec4_kernel<OT, WT>, a.n_tokens, threads, smem, stream, a);                   \
+    else llg_launch(qkv_row_prep_kernel<OT, WT>, a.n_tokens, threads, smem, stream, a);                            \
   } while (0)
   if (out_dtype == LLG_F32 && a.w_dtype == LLG_F32) LAUNCH(float, float);
   else if (out_dtype == LLG_F32 && a.w_dtype == LLG_BF16) LAUNCH(float, __nv_bfloat16);
@@ -892,16 +1112,7 @@ LLG_API int llg_qkv_row_prep(const QkvRowPrepArgs* args, int out_dtype, cudaStre
 
 // ---- activations of an ungated feed-forward ---------------------------------------------
 
-// out[n][i] = act(sum of the partials of in[n][i]).  Kinds: 0 relu(z)^2, 1 gelu with the tanh form
-// 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), 2 silu, 3 relu.
-__device__ __forceinline__ float llg_act(int kind, float z) {
-  switch (kind) {
-    case 0: { const float r = fmaxf(z, 0.f); return r * r; }
-    case 1: return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
-    case 2: return z / (1.0f + expf(-z));
-    default: return fmaxf(z, 0.f);
-  }
-}
+// out[n][i] = act(sum of the partials of in[n][i]); the kinds are those of llg_act (common.cuh).
 
 template <typename IT, typename OT>
 __global__ void act_rows_kernel(const IT* __restrict__ in, int n_partials, long long partial_stride, OT* __restrict__ out,

@@ -134,7 +134,27 @@ struct GemmParams {
   int gate_rows;    // gated, weights as first operand: features per block (at most 128)
   QkPrepArgs prep;  // EPI 2 / 3: what the q/k/v preparation needs (its `qkv` field is not used)
   RowScale scale;   // of the token rows of x: the result's rows are multiplied by it (EPI 2 / 3 take prep.row_scale)
+  int act;          // EPI 0, one split: 0 = none, kind + 1 = every element goes through llg_act(kind, .) before it is stored
 };
+
+// The activation of an epilogue on sixteen values.  The square of relu is two instructions a value and stays in line; the
+// other kinds are one call to code that exists once: written out at every place of the unrolled epilogues (hundreds), the
+// exponentials and their range handling made the kernel outgrow the instruction cache (a prompt product took 2.8 times as long).
+__device__ __noinline__ void act16_general(int kind, float (&v)[16]) {
+#pragma unroll 1
+  for (int c = 0; c < 16; ++c) v[c] = llg_act(kind, v[c]);
+}
+__device__ __forceinline__ void act16(int kind, float (&v)[16]) {
+  if (kind == 0) {
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      const float r = fmaxf(v[c], 0.f);
+      v[c] = r * r;
+    }
+  } else {
+    act16_general(kind, v);
+  }
+}
 
 // an element of a weight vector stored as float32 or bfloat16
 __device__ __forceinline__ float vec_elem(const void* p, int dtype, int i) {
@@ -488,6 +508,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
   #pragma unroll
                 for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r[c]) * rs;
+                if (p.act) act16(p.act - 1, v);
               }
               if (tok < p.o) {
                 if (vec_ok && f0 + 16 <= width) {
@@ -543,6 +564,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
   #pragma unroll
                   for (int c = 0; c < 16; ++c)
                     v[c] = p.scale.ss ? __uint_as_float(r[q][c]) * col_scale[c0 + 16 * q + c] : __uint_as_float(r[q][c]);
+                  if (p.act) act16(p.act - 1, v);
                   OT* dst = out + (long long)(n0 + c0 + 16 * q) * p.o + o;
   #pragma unroll
                   for (int c = 0; c < 16; ++c)
@@ -701,14 +723,31 @@ LLG_API int llg_gemm_tc_splits(int k, int splits) {
 // all features, zero rows up to P, then the up rows in the same way; out is [n][F] = silu(gate) * up.
 // `scale` (may be null): what a norm left for the rows of x; the rows of the result are multiplied by it (with several
 // splits every partial is).
+static int gemm_tc_run(const void* x, const void* w, void* out, int out_dtype, int n, int o, int k, int splits,
+                       int tile_n, int gated_features, const RowScale* scale, int act, cudaStream_t stream);
+
 LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, int n, int o, int k, int splits,
                         int tile_n, int gated_features, const RowScale* scale, cudaStream_t stream) {
+  return gemm_tc_run(x, w, out, out_dtype, n, o, k, splits, tile_n, gated_features, scale, 0, stream);
+}
+
+// out[n][o] = act(x w^T) in one split, the activation (kind as in llg_act, common.cuh) applied to the float32 sums
+// before they are rounded to the output type: the up product of an ungated feed-forward.
+LLG_API int llg_gemm_tc_act(const void* x, const void* w, void* out, int out_dtype, int n, int o, int k, int kind,
+                            const RowScale* scale, cudaStream_t stream) {
+  LLG_REQUIRE(kind >= 0 && kind < LLG_ACT_KINDS, "gemm_tc_act: activation kind %d is not known", kind);
+  return gemm_tc_run(x, w, out, out_dtype, n, o, k, 1, 0, 0, scale, kind + 1, stream);
+}
+
+static int gemm_tc_run(const void* x, const void* w, void* out, int out_dtype, int n, int o, int k, int splits,
+                       int tile_n, int gated_features, const RowScale* scale, int act, cudaStream_t stream) {
   const RowScale rs = scale ? *scale : RowScale{nullptr, 0, 0.f, 0.f};
   LLG_REQUIRE(llg_gemm_tc_supported(x, w, n, o, k), "gemm_tc: needs k %% 8 == 0 and 16-byte aligned operands (n=%d o=%d k=%d)",
               n, o, k);
   splits = llg_gemm_tc_splits(k, splits);
   LLG_REQUIRE(out_dtype == LLG_F32 || (out_dtype == LLG_BF16 && splits == 1), "gemm_tc: bfloat16 output needs one split");
   const bool gated = gated_features > 0;
+  LLG_REQUIRE(act == 0 || (splits == 1 && !gated), "gemm_tc: an activation needs one split and no gating");
   LLG_REQUIRE(!gated || (splits == 1 && o == ((gated_features + BM - 1) / BM) * 2 * BM),
               "gemm_tc: the gated epilogue needs one split and ceil(features / 128) * 256 rows of w (features=%d rows=%d splits=%d)",
               gated_features, o, splits);
@@ -717,7 +756,7 @@ LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, 
   if (n >= 256 && tile_n <= 0) {
     // ---- prompt steps: activations are the first operand (128 tokens per tile), up to 256 features per tile ----
     // in this orientation the kernel's first-operand rows (field o) are the tokens, the second's (field n) the features
-    GemmParams ps{out, /*n=*/o, /*o=*/n, k, (nkb + splits - 1) / splits, gated_features, o / 2, BM, QkPrepArgs{}, rs};
+    GemmParams ps{out, /*n=*/o, /*o=*/n, k, (nkb + splits - 1) / splits, gated_features, o / 2, BM, QkPrepArgs{}, rs, act};
     // Tile shape: blocks run in rounds of one per SM (148 on a B200); a round costs its tile's width, and a narrower tile can save a
     // round (4096 features: 16 tiles of 256 in two token rows of 8 are 128 blocks, 18 of 240 are 144).  Two token
     // tiles per block halve the weight traffic per flop (worth about 15 %) but double the tile.
@@ -777,7 +816,7 @@ LLG_API int llg_gemm_tc(const void* x, const void* w, void* out, int out_dtype, 
     if (gate_rows < 16) gate_rows = 16;
     if (gate_rows > BM) gate_rows = BM;
   }
-  GemmParams p{out, n, o, k, (nkb + splits - 1) / splits, gated_features, o / 2, gate_rows, QkPrepArgs{}, rs};
+  GemmParams p{out, n, o, k, (nkb + splits - 1) / splits, gated_features, o / 2, gate_rows, QkPrepArgs{}, rs, act};
   LLG_REQUIRE(splits <= 65535, "gemm_tc: grid too large");
   LLG_REQUIRE(tensor_map(w, o, k, gated ? gate_rows : BM, &map_w) && tensor_map(x, n, k, tile_n, &map_x),
               "gemm_tc: cuTensorMapEncodeTiled failed or is not available");

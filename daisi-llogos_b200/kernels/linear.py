@@ -87,6 +87,22 @@ def linear(ctx, x: torch.Tensor, w: torch.Tensor, name: str, out_dtype: torch.dt
     return out
 
 
+def activated_linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str) -> None:
+    """out[n, o] = act(x . w_o), rounded to ``out``'s type once.  Where the tensor-core product would not split its
+    sums anyway (prompt steps, and decode steps of matrices with tiles enough for every multiprocessor) the activation is
+    the product's epilogue; otherwise the product leaves float32 partial sums and one kernel adds them up, applies the
+    activation and rounds."""
+    ops = ctx.ops
+    n, k = x.shape
+    o = w.shape[0]
+    tc = getattr(ops, "gemm_tc_supported", None)
+    if tc is not None and tc(x, w) and hasattr(ops, "gemm_tc_act") and \
+            ops.gemm_tc_splits(k, plan_splits(n, o, k, ops.sm_count())) == 1:
+        ops.gemm_tc_act(x, w, out, kind)
+        return
+    ops.act_rows(linear(ctx, x, w, "ffn.up", torch.float32), out, kind)
+
+
 _GATED_CHUNK = 16384   # rows per pass of the two-kernel path, bounds its [rows, 2I] scratch
 
 

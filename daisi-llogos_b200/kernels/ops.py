@@ -241,6 +241,8 @@ def _load_lib(name: str):
         lib.llg_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                     POINTER(_RowScale), c_void_p]
         lib.llg_gemm_tc_qkv.argtypes = [c_void_p, c_void_p, c_int, c_int, POINTER(_QkPrepArgs), c_void_p]
+        lib.llg_gemm_tc_act.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                        POINTER(_RowScale), c_void_p]
     elif name == "attention_simt":
         lib.llg_attn_prefill_simt.argtypes = [POINTER(_PrefillArgs), c_int, c_void_p]
         lib.llg_attn_decode_simt.argtypes = [POINTER(_DecodeArgs), c_void_p, c_int, c_void_p]
@@ -400,6 +402,19 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, tile_n: int 
         raise KernelError(f"gemm_tc: {s} splits cannot be had for k = {k}")
     _check(lib, lib.llg_gemm_tc(_ptr(x, torch.bfloat16), _ptr(w, torch.bfloat16), _ptr(out), _dt(out), n, o, k, s,
                                 tile_n, gated_features, _scale_ref(row_scale, n), _stream()))
+
+
+def gemm_tc_act(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str, row_scale: Optional[RowScale] = None) -> None:
+    """out[n, o] = act(x[n, k] w[o, k]) on the tensor cores in one split: the activation (one of ``ACTIVATIONS``) is the
+    product's epilogue, applied to the float32 sums before they are rounded to ``out``'s type."""
+    lib = _lib("gemm_tc")
+    n, k = x.shape
+    o, k2 = w.shape
+    assert k == k2 and out.shape == (n, o), (x.shape, w.shape, out.shape)
+    if kind not in ACTIVATIONS:
+        raise KernelError(f"gemm_tc_act: activation '{kind}' is not known ({', '.join(ACTIVATIONS)})")
+    _check(lib, lib.llg_gemm_tc_act(_ptr(x, torch.bfloat16), _ptr(w, torch.bfloat16), _ptr(out), _dt(out), n, o, k,
+                                    ACTIVATIONS[kind], _scale_ref(row_scale, n), _stream()))
 
 
 def gemm_tc_status() -> int:

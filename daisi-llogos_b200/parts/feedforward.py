@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import torch
 
-from ..kernels.linear import gated_layout, gated_linear, linear
+from ..kernels.linear import activated_linear, gated_layout, gated_linear, linear
 from .base import Branch, FeedForward, TensorDecl, register_part
 
 
@@ -47,9 +47,8 @@ class SwiGLU(FeedForward):
 
 class DenseMLP(FeedForward):
     """``down(act(up(x)))`` without a gate and without biases.  params: hidden_size, intermediate_size, activation
-    (one of ``ops.ACTIVATIONS``: "relu2" = the square of relu, "gelu_tanh", "silu", "relu").  The up product leaves
-    float32 sums (in parts when it splits them); one kernel adds them up, applies the activation and rounds to the
-    compute type once."""
+    (one of ``ops.ACTIVATIONS``: "relu2" = the square of relu, "gelu_tanh", "silu", "relu").  The activation sees the
+    up product's float32 sums and its result is rounded to the compute type once (``kernels.linear.activated_linear``)."""
 
     def __init__(self, params, prefix, env):
         super().__init__(params, prefix, env)
@@ -69,9 +68,8 @@ class DenseMLP(FeedForward):
         self.w_up, self.w_down = tensors["up_proj.weight"], tensors["down_proj.weight"]
 
     def forward(self, x, ctx) -> Branch:
-        z = linear(ctx, x, self.w_up, "ffn.up", torch.float32)
         act = ctx.buffer("ffn.act", (x.shape[0], self.inter))
-        ctx.ops.act_rows(z, act, self.activation)
+        activated_linear(ctx, x, self.w_up, act, self.activation)
         return Branch(linear(ctx, act, self.w_down, "ffn.out", torch.float32))
 
 

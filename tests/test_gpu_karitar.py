@@ -409,3 +409,21 @@ def test_greedy_generation_through_the_entry_point(models, dtype):
             slack = 1e-4 if dtype == torch.float32 else 0.05
             assert float(lg[tok]) >= float(lg.max()) - slack * float(lg.abs().max()), (len(toks), tok)
             toks.append(tok)
+
+
+@pytest.mark.parametrize("kind", ["relu2", "gelu_tanh"])
+@pytest.mark.parametrize("n,o,k", [(5, 200, 96), (40, 333, 128), (300, 520, 192), (700, 130, 64)])
+def test_product_with_the_activation_as_its_epilogue(llogos, kind, n, o, k):
+    """Few rows (weights are the tensor cores' rows) and many (tokens are): act(x w^T) against the plain product."""
+    from importlib import import_module
+    ops = import_module("daisi-llogos_b200.kernels.ops")
+    g = torch.Generator().manual_seed(n + o)
+    x = torch.randn((n, k), generator=g).to(torch.bfloat16)
+    w = (torch.randn((o, k), generator=g) / math.sqrt(k)).to(torch.bfloat16)
+    z = x.double() @ w.double().t()
+    want = torch.relu(z) ** 2 if kind == "relu2" else 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 5e-3)):
+        out = torch.empty((n, o), dtype=dtype, device="cuda")
+        ops.gemm_tc_act(x.cuda(), w.cuda(), out, kind)
+        assert float((out.cpu().double() - want).abs().max()) < tol * float(want.abs().max()), (dtype, n, o, k)
+    assert ops.gemm_tc_status() == 0
