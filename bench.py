@@ -411,6 +411,15 @@ def _kernel_cost(name, args, kw, keys_read):
         nkv, vd = kp.shape[1], vp.shape[3]
         pairs, rows = keys_read
         return rows * nkv * (hd + vd) * q.element_size() + 2 * q.nbytes, 2.0 * nh * (hd + vd) * pairs
+    if name in ("add_rmsnorm", "hc_add_rmsnorm"):
+        # the residual (one array or several streams) is read and, with a branch, written back; only the rows that
+        # are normalised are touched
+        residual, branch = args[0], args[1]
+        out = args[4] if name == "add_rmsnorm" else args[7]
+        m, h = out.shape
+        streams = residual.shape[0] if residual.dim() == 3 else 1
+        per_row = 4 * h * streams * (2 if branch is not None else 1) + (4 * h * branch.shape[0] if branch is not None else 0)
+        return m * (per_row + h * out.element_size()), 0.0
     if name in ("qk_prep", "qkv_row_prep", "kv_write"):
         # the page stores are arguments, but only the step's rows of them are written
         moved = sum(t.nbytes for t in tensors if t.dim() != 4)

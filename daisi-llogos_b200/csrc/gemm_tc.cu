@@ -134,7 +134,8 @@ struct GemmParams {
   int gate_rows;    // gated, weights as first operand: features per block (at most 128)
   QkPrepArgs prep;  // EPI 2 / 3: what the q/k/v preparation needs (its `qkv` field is not used)
   RowScale scale;   // of the token rows of x: the result's rows are multiplied by it (EPI 2 / 3 take prep.row_scale)
-  int act;          // EPI 0, one split: 0 = none, kind + 1 = every element goes through llg_act(kind, .) before it is stored
+  int act;          // EPI -1 (the plain epilogue with an activation; one split): kind + 1, every element goes through
+                    // llg_act(kind, .) before it is stored.  A variant of its own, so that the plain products carry none of it.
 };
 
 // The activation of an epilogue on sixteen values.  The square of relu is two instructions a value and stays in line; the
@@ -508,7 +509,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
   #pragma unroll
                 for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r[c]) * rs;
-                if (p.act) act16(p.act - 1, v);
+                if (EPI == -1) act16(p.act - 1, v);
               }
               if (tok < p.o) {
                 if (vec_ok && f0 + 16 <= width) {
@@ -537,7 +538,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
               }
             }
           }
-        } else if (EPI == 0) {
+        } else if (EPI <= 0) {
           // Up to 64 columns of the accumulator are asked for before their arrival is waited for: one trip to tensor
           // memory per 64 tokens instead of one per 16.
           constexpr int CH = TN < 64 ? TN : 64;
@@ -564,7 +565,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
   #pragma unroll
                   for (int c = 0; c < 16; ++c)
                     v[c] = p.scale.ss ? __uint_as_float(r[q][c]) * col_scale[c0 + 16 * q + c] : __uint_as_float(r[q][c]);
-                  if (p.act) act16(p.act - 1, v);
+                  if (EPI == -1) act16(p.act - 1, v);
                   OT* dst = out + (long long)(n0 + c0 + 16 * q) * p.o + o;
   #pragma unroll
                   for (int c = 0; c < 16; ++c)
@@ -747,7 +748,8 @@ static int gemm_tc_run(const void* x, const void* w, void* out, int out_dtype, i
   splits = llg_gemm_tc_splits(k, splits);
   LLG_REQUIRE(out_dtype == LLG_F32 || (out_dtype == LLG_BF16 && splits == 1), "gemm_tc: bfloat16 output needs one split");
   const bool gated = gated_features > 0;
-  LLG_REQUIRE(act == 0 || (splits == 1 && !gated), "gemm_tc: an activation needs one split and no gating");
+  LLG_REQUIRE(act == 0 || (splits == 1 && !gated && out_dtype == LLG_BF16),
+              "gemm_tc: an activation needs one split, no gating and bfloat16 output");
   LLG_REQUIRE(!gated || (splits == 1 && o == ((gated_features + BM - 1) / BM) * 2 * BM),
               "gemm_tc: the gated epilogue needs one split and ceil(features / 128) * 256 rows of w (features=%d rows=%d splits=%d)",
               gated_features, o, splits);
@@ -790,6 +792,13 @@ static int gemm_tc_run(const void* x, const void* w, void* out, int out_dtype, i
       GOS(192, __nv_bfloat16, 1);
     }
 #define GO2(W, OTT) return launch<W, 3, OTT, 2, 0, 1>(&map_x, &map_w, ps, splits, stream)
+    if (act) {
+      if (best_w == 256) GOS(256, __nv_bfloat16, -1);
+      if (best_w == 240) GOS(240, __nv_bfloat16, -1);
+      if (best_w == 224) GOS(224, __nv_bfloat16, -1);
+      if (best_w == 208) return launch<208, 3, __nv_bfloat16, 2, -1, 1>(&map_x, &map_w, ps, splits, stream);
+      return launch<176, 3, __nv_bfloat16, 2, -1, 1>(&map_x, &map_w, ps, splits, stream);
+    }
     if (out_dtype == LLG_F32) {
       if (best_w == 256) GOS(256, float, 0);
       if (best_w == 240) GOS(240, float, 0);
@@ -832,9 +841,11 @@ static int gemm_tc_run(const void* x, const void* w, void* out, int out_dtype, i
     return out_dtype == LLG_F32 ? launch<TN, ST2, float, 2, 1, 0>(mw, mx, p, splits, stream)            \
                                 : launch<TN, ST2, __nv_bfloat16, 2, 1, 0>(mw, mx, p, splits, stream)
 #define PLAIN(TN, ST1)                                                                               \
+  if (act) return launch<TN, ST1, __nv_bfloat16, 1, -1, 0>(mw, mx, p, splits, stream);                  \
   return out_dtype == LLG_F32 ? launch<TN, ST1, float, 1, 0, 0>(mw, mx, p, splits, stream)              \
                               : launch<TN, ST1, __nv_bfloat16, 1, 0, 0>(mw, mx, p, splits, stream)
 #define WIDE(TN, ST2)                                                                                \
+  if (wide && act) return launch<TN, ST2, __nv_bfloat16, 2, -1, 0>(mw, mx, p, splits, stream);          \
   if (wide)                                                                                           \
     return out_dtype == LLG_F32 ? launch<TN, ST2, float, 2, 0, 0>(mw, mx, p, splits, stream)            \
                                 : launch<TN, ST2, __nv_bfloat16, 2, 0, 0>(mw, mx, p, splits, stream)

@@ -96,7 +96,7 @@ def activated_linear(ctx, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, k
     n, k = x.shape
     o = w.shape[0]
     tc = getattr(ops, "gemm_tc_supported", None)
-    if tc is not None and tc(x, w) and hasattr(ops, "gemm_tc_act") and \
+    if tc is not None and tc(x, w) and out.dtype == torch.bfloat16 and hasattr(ops, "gemm_tc_act") and \
             ops.gemm_tc_splits(k, plan_splits(n, o, k, ops.sm_count())) == 1:
         ops.gemm_tc_act(x, w, out, kind)
         return

@@ -406,14 +406,14 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, *, tile_n: int 
 
 def gemm_tc_act(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, kind: str, row_scale: Optional[RowScale] = None) -> None:
     """out[n, o] = act(x[n, k] w[o, k]) on the tensor cores in one split: the activation (one of ``ACTIVATIONS``) is the
-    product's epilogue, applied to the float32 sums before they are rounded to ``out``'s type."""
+    product's epilogue, applied to the float32 sums before they are rounded to ``out`` (bfloat16)."""
     lib = _lib("gemm_tc")
     n, k = x.shape
     o, k2 = w.shape
     assert k == k2 and out.shape == (n, o), (x.shape, w.shape, out.shape)
     if kind not in ACTIVATIONS:
         raise KernelError(f"gemm_tc_act: activation '{kind}' is not known ({', '.join(ACTIVATIONS)})")
-    _check(lib, lib.llg_gemm_tc_act(_ptr(x, torch.bfloat16), _ptr(w, torch.bfloat16), _ptr(out), _dt(out), n, o, k,
+    _check(lib, lib.llg_gemm_tc_act(_ptr(x, torch.bfloat16), _ptr(w, torch.bfloat16), _ptr(out, torch.bfloat16), _dt(out), n, o, k,
                                     ACTIVATIONS[kind], _scale_ref(row_scale, n), _stream()))
 
 

@@ -39,6 +39,11 @@ CONFIGS = {
     # no streams at all (the ordinary residual), no loop, heads of 48 and 32 (the mma.sync kernels in bfloat16)
     "plain_residual": config([layer(attention(4, 2, 48, 48, 20), 64), layer(attention(8, 8, 32, 32, 5), 120)],
                              vocab=190, width=96, streams=None),
+    # sizes that fit no vector access and no tensor-core tile: a width that is no multiple of 8, three heads, heads of 20
+    # and 12; twelve query heads on one key/value head; a window of one token (a position sees itself only); a loop
+    # that runs once
+    "odd": config([layer(attention(12, 1, 16, 16, 1), 50), layer(attention(3, 1, 20, 12, None), None),
+                   layer(attention(5, 5, 8, 8, 200), 30)], vocab=97, width=100, streams=2, loop=(1, 3, 1)),
     # four streams, heads of 128, a loop over everything
     "four": config([layer(attention(2, 1, 128, 128, 100), 200)], vocab=150, width=80, streams=4, loop=(0, 1, 2)),
 }
