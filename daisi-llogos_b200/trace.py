@@ -27,7 +27,7 @@ from .engine.engine import Engine
 from .weights.loader import load_model
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
-_SPARE_REQUESTS = 256     # pages beyond --max-tokens, one per request that may be alive (see main)
+_SPARE_REQUESTS = 256     # most requests alive at once: slots, and pages beyond --max-tokens, one each (see main)
 
 
 def _longest(model, tokens: int) -> int:
@@ -57,7 +57,7 @@ def main(argv=None) -> int:
     spare = min(pages, _SPARE_REQUESTS)
     # the longest single request: what the cache holds, or the model's position limit where that is less
     engine = Engine(model, max_tokens=(pages + spare) * 64, max_seq_len=_longest(model, pages * 64),
-                    n_slots=max(1, min(pages, 1024)), use_graphs=not args.no_graphs)
+                    n_slots=max(1, spare), use_graphs=not args.no_graphs)
     pages += spare
     print(f"[trace_run] ready: cache of {pages} pages of 64 tokens ({engine.cache.bytes() / 2**20:.1f} MiB)",
           file=sys.stderr, flush=True)

@@ -154,7 +154,8 @@ def _plain_attention(q, k, v, gate, scale, window, sink):
 def test_attention_kernels_with_sink_gate_and_standing_out_keys(llogos, dtype, nh, nkv, hd, vd, window):
     """One sequence of 300 tokens, a prompt step over all of it and a decode step for its last token.  In every head the
     key just inside the last queries' window and the key just outside it are made to stand out (a multiple of the query),
-    so that a window that is one token off, or a sink that is left out, changes the output by far more than the bound."""
+    so that a window that is one token off, or a sink that is left out, changes the output by far more than the bound;
+    without a window the key that stands out lies hundreds of positions back."""
     from importlib import import_module
     ops = import_module("daisi-llogos_b200.kernels.ops")
     g = torch.Generator().manual_seed(nh * 1000 + hd + vd)
@@ -165,8 +166,11 @@ def test_attention_kernels_with_sink_gate_and_standing_out_keys(llogos, dtype, n
     gate = torch.rand((t, nh), generator=g)
     scale = 0.7 / math.sqrt(hd)
     for qi in (t - 1, t - 2, 200):
-        lo = qi - window + 1 if window else 0
-        for pos, sign in ((lo, 1.0), (lo - 1, 1.0), (0, -1.0)):
+        if window:
+            marked = ((qi - window + 1, 1.0), (qi - window, 1.0), (0, -1.0))
+        else:
+            marked = ((t - qi + 1, 1.0),)          # no window: a key hundreds of positions back, one per marked query
+        for pos, sign in marked:
             if 0 <= pos < qi:
                 k[pos] = sign * 6.0 * q[qi, ::nh // nkv] / math.sqrt(hd)
     rnd = (lambda x: x.to(dtype).float())
@@ -390,6 +394,42 @@ def test_a_key_that_stands_out_at_every_windows_edge(llogos, tmp_path, dtype):
         t_in[inside], t_out[outside] = b_tok, b_tok
         r_in, r_out = KP.forward(wf, cfg, t_in)[inside], KP.forward(wf, cfg, t_out)[outside]
         assert float((r_in - r_out).abs().max()) > 0.15 * float(r_in.abs().max())
+
+
+@pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
+def test_a_far_key_among_hundreds(llogos, tmp_path, dtype):
+    """The same construction without a window: token a stands at position 2, token b 330 positions later (five pages on);
+    b's logits with a there and with another token in a's place are far apart, in a prompt and decoded."""
+    cfg = KM.config([KM.layer(KM.attention(2, 1, 32, 32, None, scale=2.0), None)], vocab=50, width=48, streams=2)
+    w = KM.random_weights(cfg, 78)
+    a_tok, b_tok = 11, 12
+    gen = torch.Generator().manual_seed(3)
+    perm = torch.randperm(48, generator=gen)
+    w["embed"][a_tok] = (2 * torch.randn(48, generator=gen)).to(torch.bfloat16)
+    w["embed"][b_tok] = w["embed"][a_tok][perm]
+    w["l0.mix.k"][:, perm] = w["l0.mix.q"][:32]
+    w["l0.mix.k.b"][:] = w["l0.mix.q.b"][:32]
+    w["l0.mix.k.norm"][:] = w["l0.mix.q.norm"][:32]
+    d = str(tmp_path / "far")
+    KM.write_model(llogos, d, cfg, 0, weights=w)
+    wf = {k: v.float() for k, v in w.items()}
+    model = llogos.weights.load_model(d, dtype=dtype, device="cuda:0")
+    eng = llogos.engine.Engine(model, max_tokens=64 * 8)
+    toks = torch.randint(13, 50, (336,), generator=gen).tolist()
+    b_at = 332
+    toks[b_at] = b_tok
+    with_a, without_a = list(toks), list(toks)
+    with_a[2] = a_tok
+    refs = [KP.forward(wf, cfg, t) for t in (with_a, without_a)]
+    assert float((refs[0][b_at] - refs[1][b_at]).abs().max()) > 0.1 * float(refs[0][b_at].abs().max())
+    for t, ref in zip((with_a, without_a), refs):
+        for cut in (len(t), b_at):
+            slot = eng.open()
+            lg = eng.step([(slot, t[:cut])], [[b_at] if b_at < cut else []])
+            if b_at >= cut:
+                lg = eng.step([(slot, [t[b_at]])])
+            close(lg, ref[b_at:b_at + 1], dtype, ("far key", cut))
+            eng.close(slot)
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
