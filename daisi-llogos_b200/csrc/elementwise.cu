@@ -17,7 +17,7 @@ LLG_API int llg_page_size() { return LLG_PAGE; }
 
 template <typename TT>
 __global__ void embed_rows_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
-                                  float* __restrict__ out, int hidden, int vocab) {
+                                  float* __restrict__ out, int hidden, int vocab, int copies, long long copy_stride) {
   pdl_launch_dependents();
   pdl_wait();
   const int n = blockIdx.x;
@@ -25,23 +25,34 @@ __global__ void embed_rows_kernel(const TT* __restrict__ table, const int* __res
   if (id < 0 || id >= vocab) id = 0;  // ids are validated on the host; never read out of range
   const TT* row = table + (long long)id * hidden;
   float* o = out + (long long)n * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_f32(row[i]);
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = to_f32(row[i]);
+    for (int c = 0; c < copies; ++c) o[c * copy_stride + i] = v;
+  }
 }
 
 // residual[n][:] = table[ids[n]][:]   (no scaling; Inference/ForwardPass.cs:205)
-LLG_API int llg_embed_rows(const void* table, int table_dtype, const int* ids, float* out,
-                           int n_tokens, int hidden, int vocab, cudaStream_t stream) {
-  LLG_REQUIRE(n_tokens >= 0 && hidden > 0 && vocab > 0, "embed_rows: bad sizes n=%d hidden=%d vocab=%d",
-              n_tokens, hidden, vocab);
+// With copies > 1 the row is written `copies` times, `copy_stride` elements apart (a residual of several streams that all
+// start as the embedding: out is [copies][n_tokens][hidden]).
+LLG_API int llg_embed_rows_copies(const void* table, int table_dtype, const int* ids, float* out, int n_tokens, int hidden,
+                                  int vocab, int copies, long long copy_stride, cudaStream_t stream) {
+  LLG_REQUIRE(n_tokens >= 0 && hidden > 0 && vocab > 0 && copies >= 1, "embed_rows: bad sizes n=%d hidden=%d vocab=%d copies=%d",
+              n_tokens, hidden, vocab, copies);
   if (n_tokens == 0) return 0;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == LLG_F32)
-    llg_launch(embed_rows_kernel<float>, n_tokens, threads, 0, stream, (const float*)table, ids, out, hidden, vocab);
+    llg_launch(embed_rows_kernel<float>, n_tokens, threads, 0, stream, (const float*)table, ids, out, hidden, vocab, copies, copy_stride);
   else if (table_dtype == LLG_BF16)
-    llg_launch(embed_rows_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab);
+    llg_launch(embed_rows_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab,
+               copies, copy_stride);
   else
     return llg_fail("embed_rows: unknown table dtype %d", table_dtype);
   return llg_check_launch("embed_rows");
+}
+
+LLG_API int llg_embed_rows(const void* table, int table_dtype, const int* ids, float* out,
+                           int n_tokens, int hidden, int vocab, cudaStream_t stream) {
+  return llg_embed_rows_copies(table, table_dtype, ids, out, n_tokens, hidden, vocab, 1, 0, stream);
 }
 
 // four consecutive elements as float32 (the address is a multiple of 4 elements)
@@ -713,7 +724,8 @@ LLG_API int llg_zero_rows(void* base, const int* rows, int n_rows, long long row
 
 // See HyperNormArgs in kernel_args.h.  One block per output row; the read-out u stays in shared memory between the
 // pass that updates the streams and the pass that writes the normalised row.
-constexpr int HC_MAX = 8;     // most streams
+constexpr int HC_MAX = 16;    // most streams (the vector kernel holds up to HC_VEC_MAX of them in registers)
+constexpr int HC_VEC_MAX = 8;
 
 template <typename OT, typename WT>
 __global__ void hc_add_rmsnorm_kernel(HyperNormArgs a) {
@@ -723,7 +735,7 @@ __global__ void hc_add_rmsnorm_kernel(HyperNormArgs a) {
   __shared__ float c_mix[HC_MAX * HC_MAX], c_write[HC_MAX], c_read[HC_MAX];
   const int S = a.n_streams;
   // the connection's weights are no result of this step: fetched while the kernel ahead still runs
-  if (threadIdx.x < S * S) c_mix[threadIdx.x] = a.branch ? a.mix[threadIdx.x] : 0.f;
+  for (int i = threadIdx.x; i < S * S; i += blockDim.x) c_mix[i] = a.branch ? a.mix[i] : 0.f;
   if (threadIdx.x < S) {
     c_write[threadIdx.x] = a.branch ? a.write[threadIdx.x] : 0.f;
     c_read[threadIdx.x] = a.read ? a.read[threadIdx.x] : 1.f;
@@ -783,7 +795,7 @@ __global__ void __launch_bounds__(512) hc_add_rmsnorm_vec4_kernel(HyperNormArgs 
   __shared__ float c_mix[HC_MAX * HC_MAX], c_write[HC_MAX], c_read[HC_MAX];
   const int S = a.n_streams;
   const int nv = a.hidden >> 2;
-  if (threadIdx.x < S * S) c_mix[threadIdx.x] = a.branch ? a.mix[threadIdx.x] : 0.f;
+  for (int i = threadIdx.x; i < S * S; i += blockDim.x) c_mix[i] = a.branch ? a.mix[i] : 0.f;
   if (threadIdx.x < S) {
     c_write[threadIdx.x] = a.branch ? a.write[threadIdx.x] : 0.f;
     c_read[threadIdx.x] = a.read ? a.read[threadIdx.x] : 1.f;
@@ -898,7 +910,7 @@ LLG_API int llg_hc_add_rmsnorm(const HyperNormArgs* args, cudaStream_t stream) {
       vpt = (nv + threads - 1) / threads;
     }
   }
-  const bool vec_ok = vec && vpt <= 4;
+  const bool vec_ok = vec && vpt <= 4 && a.n_streams <= HC_VEC_MAX;
 #define LAUNCH_V(OT, WT, SM)                                                                                        \
   do {                                                                                                              \
     if (vpt <= 1) llg_launch(hc_add_rmsnorm_vec4_kernel<OT, WT, 1, SM>, a.n_out, threads, 0, stream, a);            \
@@ -910,7 +922,7 @@ LLG_API int llg_hc_add_rmsnorm(const HyperNormArgs* args, cudaStream_t stream) {
     if (vec_ok) {                                                                                                   \
       if (a.n_streams <= 2) LAUNCH_V(OT, WT, 2);                                                                    \
       else if (a.n_streams <= 4) LAUNCH_V(OT, WT, 4);                                                               \
-      else LAUNCH_V(OT, WT, HC_MAX);                                                                                \
+      else LAUNCH_V(OT, WT, HC_VEC_MAX);                                                                            \
       break;                                                                                                        \
     }                                                                                                               \
     if (smem > 48 * 1024) {                                                                                         \

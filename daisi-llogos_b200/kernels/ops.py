@@ -220,6 +220,7 @@ def _load_lib(name: str):
         if lib.llg_page_size() != PAGE:
             raise KernelError(f"the kernels use pages of {lib.llg_page_size()} tokens, Python expects {PAGE}")
         lib.llg_embed_rows.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+        lib.llg_embed_rows_copies.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_longlong, c_void_p]
         lib.llg_add_rmsnorm.argtypes = [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_float,
                                         c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]
         lib.llg_qk_prep.argtypes = [POINTER(_QkPrepArgs), c_int, c_void_p]
@@ -296,10 +297,17 @@ def require_gpu() -> None:
 # ---- kernels ------------------------------------------------------------------------
 
 def embed_rows(table: torch.Tensor, token_ids: torch.Tensor, out_residual: torch.Tensor) -> None:
-    """out_residual[n] = table[token_ids[n]] as float32."""
+    """out_residual[n] = table[token_ids[n]] as float32; a residual of several streams ``[S, N, hidden]`` gets the row in
+    every stream."""
     lib = _lib("elementwise")
     vocab, hidden = table.shape
     n = token_ids.numel()
+    if out_residual.dim() == 3:
+        assert out_residual.shape[1:] == (n, hidden)
+        _check(lib, lib.llg_embed_rows_copies(_ptr(table), _dt(table), _ptr(token_ids, torch.int32),
+                                              _ptr(out_residual, torch.float32), n, hidden, vocab, out_residual.shape[0],
+                                              n * hidden, _stream()))
+        return
     assert out_residual.shape == (n, hidden)
     _check(lib, lib.llg_embed_rows(_ptr(table), _dt(table), _ptr(token_ids, torch.int32),
                                    _ptr(out_residual, torch.float32), n, hidden, vocab, _stream()))

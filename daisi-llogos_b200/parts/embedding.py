@@ -33,8 +33,7 @@ class TokenEmbedding(Part):
     def forward(self, ctx) -> torch.Tensor:
         if self.streams:
             residual = ctx.buffer("residual", (self.streams, ctx.n_tokens, self.hidden), torch.float32)
-            for s in range(self.streams):
-                ctx.ops.embed_rows(self.weight, ctx.token_ids, residual[s])
+            ctx.ops.embed_rows(self.weight, ctx.token_ids, residual)       # every stream starts as the embedding
             return residual
         residual = ctx.buffer("residual", (ctx.n_tokens, self.hidden), torch.float32)
         ctx.ops.embed_rows(self.weight, ctx.token_ids, residual)

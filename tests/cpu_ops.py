@@ -20,7 +20,8 @@ def require_gpu():
 
 
 def embed_rows(table, token_ids, out_residual):
-    out_residual.copy_(table[token_ids.long()].float())
+    rows = table[token_ids.long()].float()
+    out_residual.copy_(rows if out_residual.dim() == 2 else rows.expand_as(out_residual))
 
 
 def add_rmsnorm(residual, branch, weight, eps, out, rows=None):
@@ -116,7 +117,7 @@ def silu_mul(gate_up, out):
 
 
 def hc_max_streams():
-    return 8
+    return 16
 
 
 def hc_add_rmsnorm(streams, branch, mix, write, read, weight, eps, out, rows=None):

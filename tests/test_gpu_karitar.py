@@ -71,7 +71,7 @@ def tokens_for(cfg, n, seed):
 # ---- mechanisms alone --------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("streams,hidden", [(1, 40), (2, 72), (3, 96), (4, 130), (8, 64)])
+@pytest.mark.parametrize("streams,hidden", [(1, 40), (2, 72), (3, 96), (4, 130), (8, 64), (8, 1024), (11, 64), (16, 48)])
 def test_stream_norm_kernel(llogos, dtype, streams, hidden):
     from importlib import import_module
     ops = import_module("daisi-llogos_b200.kernels.ops")
