@@ -135,3 +135,7 @@ register_architecture("Qwen3ForCausalLM", _dense_reader(qk_norm=True, force_bias
 from . import karitar as _karitar  # noqa: E402  (its module needs the part specs imported above)
 
 register_architecture(_karitar.NAME, _karitar.KaritarConfig.from_dict, _karitar.karitar_spec)
+
+from . import fipavik as _fipavik  # noqa: E402
+
+register_architecture(_fipavik.NAME, _fipavik.FipavikConfig.from_dict, _fipavik.fipavik_spec)

@@ -21,6 +21,8 @@ from ..parts import embedding as _embedding  # noqa: F401
 from ..parts import feedforward as _feedforward  # noqa: F401
 from ..parts import gated_attention as _gated_attention  # noqa: F401
 from ..parts import hyper as _hyper  # noqa: F401
+from ..parts import latent_attention as _latent_attention  # noqa: F401
+from ..parts import moe as _moe  # noqa: F401
 from ..parts import norm as _norm  # noqa: F401
 from ..parts import position as _position  # noqa: F401
 
@@ -49,7 +51,7 @@ class DecoderModel:
                 if family not in part_families():
                     raise ValueError(f"layers[{l_i}].{role}: '{family}' is not a part family ({', '.join(part_families())})")
                 parts[role] = part_class(family, ps.kind)(ps.params, ps.prefix, self.env)
-            self.blocks.append(block_cls({}, "", self.env, parts))
+            self.blocks.append(block_cls(ls.params, "", self.env, parts))
         # an entry that reads another entry's cache: its mixer must be able to read what the owner keeps
         self._last_reader: Dict[int, int] = {}
         for e_i, e in enumerate(spec.schedule):

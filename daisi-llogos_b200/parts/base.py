@@ -46,11 +46,16 @@ class Branch:
     ``data`` is ``[n_partials, n_tokens, hidden]``; the partials (split-K slices of a
     matrix product, in float32) are summed by whoever consumes the branch.  ``write``: for a residual that is
     more than one stream, the part that holds the weights with which this branch enters the streams (set by the
-    block that arranged the sublayer; ``None`` where the branch is simply added).
+    block that arranged the sublayer; ``None`` where the branch is simply added).  ``more``: further sets of
+    partials ``[s_i, n_tokens, hidden]`` that enter the residual together with ``data`` (sublayers that read the
+    same norm's output side by side); ``scale``: the factor on the whole sum as it is added.  Only norms that say
+    so take ``more`` or a scale other than 1 (``Norm.check_plain`` is for the others).
     """
 
     data: torch.Tensor
     write: Any = None
+    more: Tuple[torch.Tensor, ...] = ()
+    scale: float = 1.0
 
     @property
     def n_partials(self) -> int:
@@ -101,9 +106,28 @@ class Part:
         return None
 
 
+def as_f32(t: torch.Tensor, env: "BuildEnv") -> torch.Tensor:
+    """A small tensor in float32 on the part's device (kernels read sinks, gains and the like as float32 whatever
+    the checkpoint stored)."""
+    if t.dtype == torch.float32:
+        return t.contiguous()
+    if t.is_cuda and hasattr(env.ops, "cast"):
+        out = torch.empty(t.shape, dtype=torch.float32, device=t.device)
+        env.ops.cast(t.contiguous(), out)
+        return out
+    return t.to(torch.float32).contiguous()
+
+
 class Norm(Part):
     def forward(self, residual, branch: Optional[Branch], ctx, rows=None) -> torch.Tensor:
         raise NotImplementedError
+
+    @staticmethod
+    def check_plain(branch: Optional[Branch], who: str) -> None:
+        """For norms that add one set of partials, unscaled: refuses a branch that asks for more."""
+        if branch is not None and (branch.more or branch.scale != 1.0):
+            raise ValueError(f"{who}: the pending branch carries several sublayers' outputs or a scale; "
+                             f"this norm adds one output as it is")
 
     def forward_unscaled(self, residual, branch: Optional[Branch], ctx, rows=None):
         """``(x, row_scale)``: like ``forward``, but the norm may leave a per-row factor to the consumer

@@ -27,6 +27,34 @@ class PreNormBlock(Block):
         return p["ffn"].forward(h, ctx, **kw)
 
 
+class ParallelBlock(Block):
+    """One norm whose output feeds the mixer and the feed-forward side by side; both outputs enter the residual
+    together, times ``residual_scale``: ``x' = x + s (mixer(h) + ffn(h))`` with ``h = norm1(x)``.  roles: norm1, mixer,
+    ffn (a layer may have no feed-forward).  The norm that adds the block's pending branch must take several sets
+    of partials and a scale (``layernorm`` does).  params: residual_scale (default 1)."""
+
+    ROLES = {"norm1": "norm", "mixer": "mixer", "ffn": "ffn"}
+
+    def __init__(self, params, prefix, env, parts):
+        super().__init__(params, prefix, env, parts)
+        for role in ("norm1", "mixer"):
+            if role not in parts:
+                raise ValueError(f"parallel block: no part for the role '{role}'")
+        self.scale = float(self.params.get("residual_scale", 1.0))
+
+    def forward(self, residual, pending: Optional[Branch], ctx, cache) -> Optional[Branch]:
+        p = self.parts
+        # neither consumer gets a row scale: both read the same finished rows
+        h = p["norm1"].forward(residual, pending, ctx)
+        a = p["mixer"].forward(h, ctx, cache)
+        if a.more or a.scale != 1.0 or a.write is not None:
+            raise ValueError("parallel block: the mixer's branch must be plain partials")
+        if "ffn" not in p:
+            return Branch(a.data, scale=self.scale)
+        f = p["ffn"].forward(h, ctx)
+        return Branch(a.data, more=(f.data,) + tuple(f.more), scale=self.scale)
+
+
 def normed_for(norm, consumer, residual, pending, ctx, rows=None):
     """``(x, keyword arguments)`` for ``consumer.forward``: a consumer that takes a row scale lets the norm leave
     its division to the consumer's first product."""
@@ -37,3 +65,4 @@ def normed_for(norm, consumer, residual, pending, ctx, rows=None):
 
 
 register_part("block", "prenorm", PreNormBlock)
+register_part("block", "parallel", ParallelBlock)

@@ -88,6 +88,8 @@ class HyperRmsNorm(Norm):
         m = residual.shape[1] if rows is None else rows.numel()
         out = ctx.buffer("norm.out", (m, self.size))
         mix = write = data = None
+        if branch is not None and (branch.more or branch.scale != 1.0):
+            raise ValueError("hyper_rmsnorm: the pending branch carries several sublayers' outputs or a scale")
         if branch is not None:
             if not isinstance(branch.write, StreamWrite) or branch.write.streams != self.streams:
                 raise ValueError("hyper_rmsnorm: the pending branch carries no write weights for these streams")

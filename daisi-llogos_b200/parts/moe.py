@@ -1,0 +1,116 @@
+"""A feed-forward of many small experts of which every token uses a few, beside an optional shared expert.
+
+Router: ``z = W_r h + b`` in float32; the ``top`` experts of largest ``z`` are chosen per token and weighted by a
+softmax over the chosen logits alone.  Every expert is the gated form ``W_down (silu(W_gate h) * W_up h)`` without
+biases; the token's output is the weighted sum of its experts' outputs, plus the shared expert's (which every token
+runs) where the layer has one.
+
+On the device the step's (token, choice) pairs are put in the order of their experts, every expert's run of rows
+filled up to a whole tile (``ops.moe_plan``), so that two grouped products (gate/up with the gating as its epilogue,
+then down) work tile by tile, each tile with one expert's matrices; ``ops.moe_combine`` adds a token's rows with their
+weights, and the shared expert's partial sums, into one float32 set of partials.  Nothing comes back to the host: the
+same launches serve any routing, so a decode step can be recorded once and replayed.
+"""
+from __future__ import annotations
+
+import torch
+
+from .base import Branch, FeedForward, TensorDecl, as_f32, part_class, register_part
+
+
+class MoeFeedForward(FeedForward):
+    """params: hidden_size, num_experts, top, expert_size (an expert's inner size), shared_size (0 or None: no shared
+    expert), router_bias (bool), shared_prefix (where the shared expert's tensors lie under this part's prefix,
+    default "shared."), shared_names (its ``tensor_names``).  Tensors: ``router.weight`` [experts, hidden],
+    ``router.bias`` [experts], and per expert i ``experts.<i>.{gate_proj,up_proj,down_proj}.weight``."""
+
+    def __init__(self, params, prefix, env):
+        super().__init__(params, prefix, env)
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.n_exp = int(p["num_experts"])
+        self.top = int(p["top"])
+        self.inter = int(p["expert_size"])
+        if not 0 < self.top <= self.n_exp:
+            raise ValueError(f"moe: top {self.top} of {self.n_exp} experts")
+        limit = getattr(env.ops, "MOE_MAX_EXPERTS", None)
+        if limit is not None and self.n_exp > limit:
+            raise ValueError(f"moe: {self.n_exp} experts; the routing kernels take up to {limit}")
+        top_limit = getattr(env.ops, "MOE_MAX_TOP", None)
+        if top_limit is not None and self.top > top_limit:
+            raise ValueError(f"moe: top {self.top}; the routing kernels take up to {top_limit}")
+        self.router_bias = bool(p.get("router_bias", False))
+        self.shared = None
+        shared = int(p.get("shared_size") or 0)
+        if shared:
+            sp = {"hidden_size": self.hidden, "intermediate_size": shared}
+            if p.get("shared_names"):
+                sp["tensor_names"] = dict(p["shared_names"])
+            self.shared_rel = str(p.get("shared_prefix", "shared."))
+            self.shared = part_class("ffn", "swiglu")(sp, prefix + self.shared_rel, env)
+        self.w_router = self.b_router = self.w_gate = self.w_up = self.w_down = None
+
+    def _expert(self, i: int, what: str) -> str:
+        return f"experts.{i}.{what}_proj.weight"
+
+    def tensor_name(self, rel: str) -> str:
+        names = self.params.get("tensor_names", {})
+        if rel in names:
+            return self.prefix + names[rel]
+        if rel.startswith("experts."):                       # "experts.<i>.gate_proj.weight" by the pattern's name
+            _, i, what = rel.split(".", 2)
+            pattern = names.get("experts.*." + what)
+            if pattern is not None:
+                return self.prefix + pattern.replace("*", i)
+        if self.shared is not None and rel.startswith("shared:"):
+            return self.shared.tensor_name(rel[len("shared:"):])
+        return self.prefix + rel
+
+    def tensors(self):
+        t = {"router.weight": TensorDecl((self.n_exp, self.hidden))}
+        if self.router_bias:
+            t["router.bias"] = TensorDecl((self.n_exp,), "bias")
+        for i in range(self.n_exp):
+            t[self._expert(i, "gate")] = TensorDecl((self.inter, self.hidden))
+            t[self._expert(i, "up")] = TensorDecl((self.inter, self.hidden))
+            t[self._expert(i, "down")] = TensorDecl((self.hidden, self.inter))
+        if self.shared is not None:
+            for rel, d in self.shared.tensors().items():
+                t["shared:" + rel] = d
+        return t
+
+    def bind(self, tensors):
+        self.w_router = as_f32(tensors["router.weight"], self.env)
+        self.b_router = as_f32(tensors["router.bias"], self.env) if self.router_bias else None
+        per = {what: [tensors[self._expert(i, what)] for i in range(self.n_exp)] for what in ("gate", "up", "down")}
+        if len({w.dtype for ws in per.values() for w in ws}) != 1:
+            raise ValueError(f"{self.prefix}: the experts' matrices are stored with different types")
+        self.w_gate = torch.stack(per["gate"]).contiguous()          # [E, inner, hidden]
+        self.w_up = torch.stack(per["up"]).contiguous()
+        self.w_down = torch.stack(per["down"]).contiguous()          # [E, hidden, inner]
+        if self.shared is not None:
+            self.shared.bind({rel[len("shared:"):]: t for rel, t in tensors.items() if rel.startswith("shared:")})
+
+    def forward(self, x, ctx) -> Branch:
+        ops = ctx.ops
+        n = x.shape[0]
+        pairs = n * self.top
+        choice = ctx.buffer("moe.choice", (n, self.top), torch.int32)
+        weight = ctx.buffer("moe.weight", (n, self.top), torch.float32)
+        ops.moe_route(x, self.w_router, self.b_router, choice, weight)
+        cap = ops.moe_row_capacity(pairs, self.n_exp)
+        row_of_pair = ctx.buffer("moe.row_of_pair", (pairs,), torch.int32)
+        token_of_row = ctx.buffer("moe.token_of_row", (cap,), torch.int32)
+        tile_expert = ctx.buffer("moe.tile_expert", (cap // ops.MOE_TILE_ROWS,), torch.int32)
+        ops.moe_plan(choice, self.n_exp, row_of_pair, token_of_row, tile_expert)
+        act = ctx.buffer("moe.act", (cap, self.inter))
+        ops.moe_gated(x, token_of_row, tile_expert, self.w_gate, self.w_up, act)
+        y = ctx.buffer("moe.y", (cap, self.hidden), torch.float32)
+        ops.moe_down(act, tile_expert, self.w_down, y)
+        shared = self.shared.forward(x, ctx).data if self.shared is not None else None
+        out = ctx.buffer("moe.out", (1, n, self.hidden), torch.float32)
+        ops.moe_combine(y, row_of_pair, weight, shared, out[0])
+        return Branch(out)
+
+
+register_part("ffn", "moe", MoeFeedForward)

@@ -37,6 +37,7 @@ class RmsNorm(Norm):
         self.weight = tensors["weight"]
 
     def forward(self, residual, branch: Optional[Branch], ctx, rows=None):
+        self.check_plain(branch, "rmsnorm")
         m = residual.shape[0] if rows is None else rows.numel()
         out = ctx.buffer("norm.out", (m, self.size))
         ctx.ops.add_rmsnorm(residual, branch.data if branch is not None else None, self.weight, self.eps, out, rows)
@@ -47,6 +48,7 @@ class RmsNorm(Norm):
         make_scale = getattr(ops, "RowScale", None)
         if make_scale is None or ctx.dtype != torch.bfloat16:
             return self.forward(residual, branch, ctx, rows), None
+        self.check_plain(branch, "rmsnorm")
         m = residual.shape[0] if rows is None else rows.numel()
         out = ctx.buffer("norm.out", (m, self.size))
         ss = ctx.buffer("norm.ss", (m, ops.norm_ss_parts(m, self.size)), torch.float32)
@@ -54,4 +56,39 @@ class RmsNorm(Norm):
         return out, make_scale(ss, self.size, self.eps)
 
 
+class LayerNorm(Norm):
+    """Layer norm fused with the residual add: ``v = residual + scale * (sum of the pending branch's partials)``,
+    ``out = (v - mean(v)) / sqrt(var(v) + eps) * weight + bias`` with the variance as the mean of the squared
+    deviations.  Takes a branch of several sublayers' outputs and a scale on their sum (``Branch.more``,
+    ``Branch.scale``).  Statistics, the residual and its sum are float32.  params: size, eps."""
+
+    def __init__(self, params, prefix, env):
+        super().__init__(params, prefix, env)
+        self.size = int(params["size"])
+        self.eps = float(params["eps"])
+        if self.eps <= 0:
+            raise ValueError("layer norm eps must be positive")
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def tensors(self):
+        return {"weight": TensorDecl((self.size,), "norm"), "bias": TensorDecl((self.size,), "bias")}
+
+    def bind(self, tensors):
+        self.weight, self.bias = tensors["weight"], tensors["bias"]
+        if self.weight.dtype != self.bias.dtype:
+            raise ValueError(f"{self.prefix}: a layer norm's weight and bias are stored with different types")
+
+    def forward(self, residual, branch: Optional[Branch], ctx, rows=None):
+        if residual.dim() != 2:
+            raise ValueError("layernorm: the residual must be one stream [tokens, hidden]")
+        m = residual.shape[0] if rows is None else rows.numel()
+        out = ctx.buffer("norm.out", (m, self.size))
+        parts = () if branch is None else (branch.data,) + tuple(branch.more)
+        ctx.ops.add_layernorm(residual, parts, branch.scale if branch is not None else 1.0, self.weight, self.bias,
+                              self.eps, out, rows)
+        return out
+
+
 register_part("norm", "rmsnorm", RmsNorm)
+register_part("norm", "layernorm", LayerNorm)

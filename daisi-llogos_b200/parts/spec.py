@@ -32,6 +32,7 @@ class LayerSpec:
 
     block: str                     # registered block kind, e.g. "prenorm"
     parts: Dict[str, PartSpec]     # role in the block -> part (the block's class names its roles)
+    params: Dict[str, Any] = field(default_factory=dict)   # the arrangement's own constants (most have none)
 
 
 @dataclass(frozen=True)

@@ -46,11 +46,22 @@ def _rows_of(page_table, ring_pages, slot, pos, kvh, nkv):
 
 def qk_prep(qkv, *, n_heads, n_kv_heads, head_dim, q_norm_w, k_norm_w, norm_eps, bias, cos, sin, rotary_dim,
             pairing, positions, q_out, k_new=None, v_new=None, k_pages=None, v_pages=None, page_table=None,
-            ring_pages=0, seq_of_token=None, slots=None):
+            ring_pages=0, seq_of_token=None, slots=None, value_dim=0, v_mix=None, v_first_in=None, v_first_out=None):
     x = qkv.float().sum(0)
     n = x.shape[0]
     nh, nkv, hd = n_heads, n_kv_heads, head_dim
-    x = x.view(n, nh + 2 * nkv, hd).clone()
+    vd = value_dim or hd
+    v_part = x[:, (nh + nkv) * hd:].reshape(n, nkv, vd).clone() if nkv else None
+    if bias is not None and nkv:
+        v_part = v_part + bias.float()[(nh + nkv) * hd:].view(1, nkv, vd)
+    if v_first_out is not None:
+        v_first_out.copy_(v_part)
+    if v_first_in is not None:
+        lam = v_mix.float().reshape(())
+        v_part = (1.0 - lam) * v_part + lam * v_first_in
+    if bias is not None:
+        bias = torch.cat([bias.float()[:(nh + nkv) * hd], torch.zeros(nkv * hd)])
+    x = torch.cat([x[:, :(nh + nkv) * hd], torch.zeros(n, nkv * hd)], dim=1).view(n, nh + 2 * nkv, hd).clone()
 
     def norm(t, w):
         return t * torch.rsqrt((t * t).mean(-1, keepdim=True) + norm_eps) * w.float()
@@ -78,7 +89,12 @@ def qk_prep(qkv, *, n_heads, n_kv_heads, head_dim, q_norm_w, k_norm_w, norm_eps,
     if nkv == 0:
         return
     k = x[:, nh:nh + nkv].to(q_out.dtype)
-    v = x[:, nh + nkv:].to(q_out.dtype)
+    v = v_part.to(q_out.dtype)
+    _store_kv(k, v, positions, k_new, v_new, k_pages, v_pages, page_table, ring_pages, seq_of_token, slots)
+
+
+def _store_kv(k, v, positions, k_new, v_new, k_pages, v_pages, page_table, ring_pages, seq_of_token, slots):
+    n, nkv = k.shape[0], k.shape[1]
     if k_new is not None:
         k_new.copy_(k)
         v_new.copy_(v)
@@ -90,6 +106,118 @@ def qk_prep(qkv, *, n_heads, n_kv_heads, head_dim, q_norm_w, k_norm_w, norm_eps,
                 pg, hh, off = _rows_of(page_table, ring_pages, slot, pos, h, nkv)
                 k_pages[pg, hh, off] = k[t, h]
                 v_pages[pg, hh, off] = v[t, h]
+
+
+def add_layernorm(residual, parts, scale, weight, bias, eps, out, rows=None):
+    idx = slice(None) if rows is None else rows.long()
+    if parts:
+        total = sum(p.sum(0) for p in parts)
+        residual[idx] += float(scale) * total[idx]
+    x = residual[idx]
+    mu = x.mean(-1, keepdim=True)
+    var = ((x - mu) ** 2).mean(-1, keepdim=True)
+    out.copy_(((x - mu) * torch.rsqrt(var + eps) * weight.float() + bias.float()).to(out.dtype))
+
+
+def latent_prep(rows, *, n_heads, head_dim, rot_dim, kv_rank, c_norm_w, norm_eps, cos, sin, positions, q_plain_out, q_out,
+                k_new=None, v_new=None, k_pages=None, v_pages=None, page_table=None, ring_pages=0, seq_of_token=None,
+                slots=None):
+    x = rows.float().sum(0)
+    n = x.shape[0]
+    qw = n_heads * (head_dim + rot_dim)
+    q = x[:, :qw].view(n, n_heads, head_dim + rot_dim)
+    c = x[:, qw:qw + kv_rank]
+    kr = x[:, qw + kv_rank:]
+    c = c * torch.rsqrt((c * c).mean(-1, keepdim=True) + norm_eps) * c_norm_w.float()
+
+    def rotate(t):                      # [..., rot_dim] with a leading token axis
+        half = rot_dim // 2
+        cs, sn = cos[positions.long()], sin[positions.long()]
+        while cs.dim() < t.dim():
+            cs, sn = cs.unsqueeze(1), sn.unsqueeze(1)
+        a, b = t[..., :half], t[..., half:]
+        return torch.cat([a * cs - b * sn, b * cs + a * sn], dim=-1)
+
+    q_plain_out.copy_(q[..., :head_dim].to(q_plain_out.dtype))
+    if rot_dim:
+        q_out[..., kv_rank:] = rotate(q[..., head_dim:]).to(q_out.dtype)
+        kr = rotate(kr)
+    k = torch.cat([c, kr], dim=-1).view(n, 1, kv_rank + rot_dim).to(q_out.dtype)
+    v = c.view(n, 1, kv_rank).to(q_out.dtype)
+    _store_kv(k, v, positions, k_new, v_new, k_pages, v_pages, page_table, ring_pages, seq_of_token, slots)
+
+
+def head_linear(x, w, y):
+    y.copy_(torch.einsum("nha,hba->nhb", x.float(), w.float()).to(y.dtype))
+
+
+MOE_TILE_ROWS = 8
+MOE_MAX_EXPERTS = 1024
+MOE_MAX_TOP = 32
+
+
+def moe_row_capacity(pairs, n_experts):
+    cap = pairs + n_experts * (MOE_TILE_ROWS - 1)
+    return -(-cap // MOE_TILE_ROWS) * MOE_TILE_ROWS
+
+
+def moe_route(x, w_router, b_router, choice, weight):
+    z = x.float() @ w_router.float().t()
+    if b_router is not None:
+        z = z + b_router.float()
+    val, idx = torch.topk(z, choice.shape[1], dim=-1)
+    choice.copy_(idx.to(torch.int32))
+    weight.copy_(torch.softmax(val, dim=-1))
+
+
+def moe_plan(choice, n_experts, row_of_pair, token_of_row, tile_expert):
+    top = choice.shape[1]
+    flat = choice.reshape(-1).tolist()
+    token_of_row.fill_(-1)
+    tile_expert.fill_(-1)
+    row = 0
+    for e in range(n_experts):
+        mine = [p for p, c in enumerate(flat) if c == e]
+        for p in reversed(mine):                 # any order inside an expert's run is allowed
+            row_of_pair[p] = row
+            token_of_row[row] = p // top
+            row += 1
+        while row % MOE_TILE_ROWS:
+            row += 1
+        for t in range((row - 1) // MOE_TILE_ROWS, -1, -1):
+            if tile_expert[t] != -1:
+                break
+            if mine:
+                tile_expert[t] = e
+        # tiles of an expert without rows stay -1 (it has none)
+
+
+def moe_gated(x, token_of_row, tile_expert, w_gate, w_up, act):
+    act.zero_()
+    for r in range(token_of_row.numel()):
+        t = int(token_of_row[r])
+        if t < 0:
+            continue
+        e = int(tile_expert[r // MOE_TILE_ROWS])
+        g = w_gate[e].float() @ x[t].float()
+        u = w_up[e].float() @ x[t].float()
+        act[r] = (g / (1 + torch.exp(-g)) * u).to(act.dtype)
+
+
+def moe_down(act, tile_expert, w_down, y):
+    y.zero_()
+    for r in range(act.shape[0]):
+        e = int(tile_expert[r // MOE_TILE_ROWS])
+        if e >= 0:
+            y[r] = w_down[e].float() @ act[r].float()
+
+
+def moe_combine(y, row_of_pair, weight, shared, out):
+    n, top = weight.shape
+    rows = row_of_pair.view(n, top).long()
+    out.copy_((weight[:, :, None] * y[rows]).sum(1))
+    if shared is not None:
+        out += shared.sum(0)
 
 
 def kv_write(k_new, v_new, k_pages, v_pages, page_table, ring_pages, positions, seq_of_token, slots,
@@ -195,8 +323,9 @@ def zero_rows(base, rows):
 
 
 class AttentionForm:
-    def __init__(self, value_dim=0, sink=None, gated=False):
+    def __init__(self, value_dim=0, sink=None, gated=False, sinks=None, chunked=False):
         self.value_dim, self.sink, self.gated = int(value_dim), sink, bool(gated)
+        self.sinks, self.chunked = sinks, bool(chunked)
 
     def plain(self, head_dim):
         return self.value_dim in (0, head_dim) and self.sink is None and not self.gated
@@ -208,10 +337,18 @@ class AttentionForm:
 PLAIN_ATTENTION = AttentionForm()
 
 
-def _attend(q, keys, vals, scale, form=PLAIN_ATTENTION, gate=None):
+def _lowest(form, window, pos):
+    """The first position a query at ``pos`` sees."""
+    if window <= 0:
+        return 0
+    return (pos // window) * window if form.chunked else max(0, pos - window + 1)
+
+
+def _attend(q, keys, vals, scale, form=PLAIN_ATTENTION, gate=None, head=0):
     s = (keys.float() @ q.float()) * scale
-    if form.sink is not None:
-        s = torch.cat([s, torch.tensor([float(form.sink)])])
+    sink = form.sink if form.sinks is None else float(form.sinks[head])
+    if sink is not None:
+        s = torch.cat([s, torch.tensor([float(sink)])])
         p = torch.softmax(s, 0)[:-1]
     else:
         p = torch.softmax(s, 0)
@@ -244,7 +381,7 @@ def attn_prefill(q, k_new, v_new, k_pages, v_pages, page_table, ring_pages, tile
         slot = int(slots[b])
         for t in range(t0, t1):
             pos = lb + (t - t0)
-            lo = max(0, pos - window + 1) if window > 0 else 0
+            lo = _lowest(form, window, pos)
             for h in range(nh):
                 kvh = h // g
                 old = [p for p in range(lo, pos + 1) if p < lb]
@@ -253,7 +390,7 @@ def attn_prefill(q, k_new, v_new, k_pages, v_pages, page_table, ring_pages, tile
                     ks.append(k_new[t0 + p - lb, kvh])
                     vs.append(v_new[t0 + p - lb, kvh])
                 o[t, h] = _attend(q[t, h], torch.stack(ks), torch.stack(vs), scale, form,
-                                  None if gate is None else gate[t, h]).to(out.dtype)
+                                  None if gate is None else gate[t, h], h).to(out.dtype)
 
 
 class _Plan:
@@ -272,12 +409,12 @@ def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, 
     o = out.view(b_n, nh, form.vd(hd))
     for b in range(b_n):
         length = int(len_before[b]) + 1
-        lo = max(0, length - window) if window > 0 else 0
+        lo = _lowest(form, window, length - 1)
         slot = int(slots[b])
         for h in range(nh):
             ks, vs = _gather(k_pages, v_pages, page_table, ring_pages, slot, range(lo, length), h // g)
             o[b, h] = _attend(q[b, h], torch.stack(ks), torch.stack(vs), scale, form,
-                              None if gate is None else gate[b, h]).to(out.dtype)
+                              None if gate is None else gate[b, h], h).to(out.dtype)
 
 
 def argmax(logits, out):
