@@ -139,8 +139,10 @@ __device__ __forceinline__ float pow2_whole(float d) {
 }
 
 // 64-key tiles that a sequence of `len` keys reads, and the first of them
-__device__ __forceinline__ int first_tile(int len, int window) { return (window > 0 ? max(0, len - window) : 0) / TK; }
-__device__ __forceinline__ int tile_count(int len, int window) { return (len + TK - 1) / TK - first_tile(len, window); }
+__device__ __forceinline__ int first_tile(int len, int window, int chunked) { return mask_first(len - 1, window, chunked) / TK; }
+__device__ __forceinline__ int tile_count(int len, int window, int chunked) {
+  return (len + TK - 1) / TK - first_tile(len, window, chunked);
+}
 
 // Where a block's run of the unit list starts: sequence, key/value head, tile within the sequence's tiles.
 struct Cursor {
@@ -212,7 +214,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         seq_len[b] = len;
         seq_slot[b] = a.slots[b];
       }
-      mine += tile_count(len, a.window);
+      mine += tile_count(len, a.window, a.chunked);
     }
     int incl = mine;
 #pragma unroll
@@ -226,7 +228,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     for (int w = 0; w < warp; ++w) before += warp_total[w];
     if (tid == 0) cum[0] = 0;
     for (int b = b0; b < b1; ++b) {
-      before += tile_count(a.len_before[b] + 1, a.window);
+      before += tile_count(a.len_before[b] + 1, a.window, a.chunked);
       cum[b + 1] = before;
     }
     __syncthreads();
@@ -253,7 +255,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         const Cursor c = locate(cum, a.n_seqs, a.nkv, u0 + idx);
         const bool staged = c.b < STAGED_SEQS;
         const int len = staged ? seq_len[c.b] : a.len_before[c.b] + 1;
-        const int tile = first_tile(len, a.window) + c.t;
+        const int tile = first_tile(len, a.window, a.chunked) + c.t;
         newest = tile == (len - 1) / TK;                 // the kernel ahead writes the newest position only
         const int page = a.page_table[(long long)(staged ? seq_slot[c.b] : a.slots[c.b]) * a.table_width + tile % a.ring_pages];
         kvh = c.kvh;
@@ -355,7 +357,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         acc.w += w * v[k].w;
       }
     }
-    if (a.has_sink) L += fast_exp2(a.sink_score * LOG2E - M);       // the sink's weight beside the keys'; it carries no value
+    if (a.has_sink) L += fast_exp2((a.sinks ? a.sinks[pend_row % a.nh] : a.sink_score) * LOG2E - M);       // the sink's weight beside the keys'; it carries no value
     float inv = L > 0.f ? 1.0f / L : 0.f;
     if (a.gate) inv *= a.gate[pend_row];
     if (live) {
@@ -382,7 +384,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int b = cur.b, kvh = cur.kvh;
     const int n_seg = min(cur.tiles - cur.t, (int)(u1 - u));
     const int len = a.len_before[b] + 1;
-    const int lo = a.window > 0 ? max(0, len - a.window) : 0;
+    const int lo = mask_first(len - 1, a.window, a.chunked);
     const int t_first = lo / TK;
     // Q^T as the second operand: column g is head g of the group, rows are head dimensions
     uint32_t qf[KSTEPS][2];
@@ -532,7 +534,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
         const long long head_row = (long long)b * a.nh + kvh * G + head;
         if (whole) {
-          if (a.has_sink) L += fast_exp2(a.sink_score * LOG2E - M);
+          if (a.has_sink) L += fast_exp2((a.sinks ? a.sinks[kvh * G + head] : a.sink_score) * LOG2E - M);
           float inv = L > 0.f ? 1.0f / L : 0.f;
           if (a.gate) inv *= a.gate[head_row];
 #pragma unroll

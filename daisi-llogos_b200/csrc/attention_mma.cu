@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_mma_kernel(PrefillArgs a)
   const int slot = a.slots[b];
   const int pos0 = lb + q_off;
   const int k_end = pos0 + nq;
-  int k_begin = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+  int k_begin = mask_first(pos0, a.window, a.chunked);
   k_begin = (k_begin / TK) * TK;
   const int n_tiles = (k_end - k_begin + TK - 1) / TK;
   const bf16* qg = (const bf16*)a.q;
@@ -217,7 +217,7 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_mma_kernel(PrefillArgs a)
     }
     // mask (only tiles that touch the diagonal or the window's edge need one), running maximum, exponentials
     float mx[2] = {-INFINITY, -INFINITY};
-    const bool need_mask = (kt + TK - 1 > pos0 + warp * 16) || (a.window > 0 && kt <= pos0 + warp * 16 + 15 - a.window);
+    const bool need_mask = (kt + TK - 1 > pos0 + warp * 16) || (a.window > 0 && kt < mask_first(pos0 + warp * 16 + 15, a.window, a.chunked));
     if (need_mask) {
 #pragma unroll
       for (int j = 0; j < 8; ++j)
@@ -226,7 +226,7 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_mma_kernel(PrefillArgs a)
           const int r = e >> 1;
           const int key = kt + j * 8 + 2 * t + (e & 1);
           const int qp = qpos0 + r * 8;
-          const bool valid = key <= qp && (a.window == 0 || key > qp - a.window);
+          const bool valid = key <= qp && key >= mask_first(qp, a.window, a.chunked);
           s[j][e] = valid ? s[j][e] : -INFINITY;
         }
     }
@@ -296,7 +296,7 @@ __global__ void __launch_bounds__(128, 3) attn_prefill_mma_kernel(PrefillArgs a)
     const int row = warp * 16 + g + r * 8;
     if (row >= nq) continue;
     float lr = l[r];
-    if (a.has_sink) lr += fast_exp2(a.sink_score * LOG2E - m[r]);   // the sink's weight beside the keys'; it carries no value
+    if (a.has_sink) lr += fast_exp2((a.sinks ? a.sinks[h] : a.sink_score) * LOG2E - m[r]);   // the sink's weight beside the keys'; it carries no value
     float inv = lr > 0.f ? 1.0f / lr : 0.f;
     if (a.gate) inv *= a.gate[(long long)(tok0 + q_off + row) * a.nh + h];
     bf16* dst = out + ((long long)(tok0 + q_off + row) * a.nh + h) * hd;
@@ -338,8 +338,8 @@ __device__ __forceinline__ uint32_t movmatrix_trans(uint32_t x) {
 constexpr int DECODE_BLOCKS_PER_SM = 2;       // blocks of this kernel that one SM holds at once
 
 // 64-key tiles that a sequence of `len` keys reads
-__device__ __forceinline__ int decode_tiles(int len, int window) {
-  const int lo = window > 0 ? max(0, len - window) : 0;
+__device__ __forceinline__ int decode_tiles(int len, int window, int chunked) {
+  const int lo = mask_first(len - 1, window, chunked);
   return (len + TK - 1) / TK - lo / TK;
 }
 
@@ -369,7 +369,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a, bf16
   int n_items = a.n_seqs * a.n_splits * a.nkv, tiles_per_item = 0;
   int my_tiles = 0;
   if (balance) {
-    my_tiles = lane < a.n_seqs ? decode_tiles(a.len_before[lane] + 1, a.window) : 0;
+    my_tiles = lane < a.n_seqs ? decode_tiles(a.len_before[lane] + 1, a.window, a.chunked) : 0;
     int hi = max(1, my_tiles);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) hi = max(hi, __shfl_xor_sync(0xffffffffu, hi, o));
@@ -410,7 +410,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a, bf16
   }
   const int len = a.len_before[b] + 1;
   const int slot = a.slots[b];
-  const int lo = a.window > 0 ? max(0, len - a.window) : 0;
+  const int lo = mask_first(len - 1, a.window, a.chunked);
   const int t0 = lo / TK, t_end = (len + TK - 1) / TK;
   const int per_split = (t_end - t0 + ns - 1) / ns;
   const int my0 = t0 + split * per_split;
@@ -640,7 +640,7 @@ __global__ void __launch_bounds__(128) attn_decode_mma_kernel(DecodeArgs a, bf16
       if (ms != -INFINITY) L += expf(ms - M) * __ldcg(&a.part_ml[(base + s) * 2 + 1]);
     }
     L = warp_sum(L);
-    if (a.has_sink) L += expf(a.sink_score - M);                    // M is in natural units here
+    if (a.has_sink) L += expf((a.sinks ? a.sinks[head] : a.sink_score) - M);                    // M is in natural units here
     float inv = L > 0.f ? 1.0f / L : 0.f;
     if (a.gate) inv *= a.gate[(long long)b * a.nh + head];
     float oacc[HDMAX / 32];

@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
   const int slot = a.slots[b];
   const int pos0 = lb + q_off;             // position of the tile's first query
   const int k_end = pos0 + nq;
-  int k_begin = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+  int k_begin = mask_first(pos0, a.window, a.chunked);     // the tile's first query sees the earliest key
   k_begin = (k_begin / KT) * KT;
   const T* q = (const T*)a.q;
 
@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
       const float* krow = Ks + lane * (hd + 1);
       float s = 0.f;
       for (int d = 0; d < hd; ++d) s = fmaf(qrow[d], krow[d], s);
-      const bool valid = qi < nq && kp < k_end && kp <= qpos && (a.window == 0 || kp > qpos - a.window);
+      const bool valid = qi < nq && kp < k_end && kp <= qpos && kp >= mask_first(qpos, a.window, a.chunked);
       s = valid ? s * a.scale : -INFINITY;
       const float m_new = fmaxf(m[i], warp_max(s));
       float corr = 1.f, p = 0.f;
@@ -144,9 +144,10 @@ __global__ void __launch_bounds__(128) attn_prefill_kernel(PrefillArgs a) {
     if (qi >= nq) continue;
     float li = l[i], keep = 1.f;
     if (a.has_sink) {                       // the sink joins the sum; the values' weights shrink with it
-      const float m_all = fmaxf(m[i], a.sink_score);
+      const float sink = a.sinks ? a.sinks[h] : a.sink_score;
+      const float m_all = fmaxf(m[i], sink);
       keep = expf(m[i] - m_all);
-      li = li * keep + expf(a.sink_score - m_all);
+      li = li * keep + expf(sink - m_all);
     }
     float inv = li > 0.f ? keep / li : 0.f;
     if (a.gate) inv *= a.gate[(long long)(tok0 + q_off + qi) * a.nh + h];
@@ -176,7 +177,7 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
 
   const int len = a.len_before[b] + 1;
   const int slot = a.slots[b];
-  const int lo = a.window > 0 ? max(0, len - a.window) : 0;
+  const int lo = mask_first(len - 1, a.window, a.chunked);
   const int t0 = lo / KT, t_end = (len + KT - 1) / KT;
   const int per_split = (t_end - t0 + a.n_splits - 1) / a.n_splits;
   const int my0 = t0 + split * per_split;
@@ -297,9 +298,11 @@ __global__ void __launch_bounds__(128) attn_decode_kernel(DecodeArgs a) {
 template <typename T>
 __global__ void attn_decode_reduce_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                           T* __restrict__ out, int nh, int hd, int n_splits, int has_sink,
-                                          float sink_score, const float* __restrict__ gate) {
+                                          float sink_score, const float* __restrict__ gate,
+                                          const float* __restrict__ sinks) {
   // (hd: elements of a value head)
   const int h = blockIdx.x, b = blockIdx.y;
+  if (sinks) sink_score = sinks[h];
   const long long base = ((long long)b * nh + h) * n_splits;
   float M = -INFINITY;
   for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
@@ -379,13 +382,13 @@ LLG_API int llg_attn_decode_simt(const DecodeArgs* args, void* out, int dtype, c
     if (e != cudaSuccess) return llg_fail("attn_decode: shared memory %zu: %s", smem, cudaGetErrorString(e));
     attn_decode_kernel<float><<<grid, 128, smem, stream>>>(a);
     attn_decode_reduce_kernel<float><<<rgrid, 64, 0, stream>>>(a.part_o, a.part_ml, (float*)out, a.nh, vd, a.n_splits,
-                                                               a.has_sink, a.sink_score, a.gate);
+                                                               a.has_sink, a.sink_score, a.gate, a.sinks);
   } else if (dtype == LLG_BF16) {
     e = cudaFuncSetAttribute(attn_decode_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return llg_fail("attn_decode: shared memory %zu: %s", smem, cudaGetErrorString(e));
     attn_decode_kernel<__nv_bfloat16><<<grid, 128, smem, stream>>>(a);
     attn_decode_reduce_kernel<__nv_bfloat16><<<rgrid, 64, 0, stream>>>(a.part_o, a.part_ml, (__nv_bfloat16*)out, a.nh, vd,
-                                                                        a.n_splits, a.has_sink, a.sink_score, a.gate);
+                                                                        a.n_splits, a.has_sink, a.sink_score, a.gate, a.sinks);
   } else {
     return llg_fail("attn_decode: unknown dtype %d", dtype);
   }
@@ -448,5 +451,7 @@ int llg_attn_decode_noalloc(const void* q, const void* k_pages, const void* v_pa
   a.has_sink = 0;
   a.sink_score = 0.f;
   a.gate = nullptr;
+  a.sinks = nullptr;
+  a.chunked = 0;
   return llg_attn_decode_simt(&a, out, dtype, stream);
 }

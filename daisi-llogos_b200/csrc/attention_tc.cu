@@ -297,7 +297,7 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(const __grid_co
       ti.pos0[g] = ti.lb + q_off + g * BQ;
     }
     // the first group's window starts earliest; the second masks the tiles that lie before its own
-    int kb = a.window > 0 ? max(0, ti.pos0[0] - a.window + 1) : 0;
+    int kb = mask_first(ti.pos0[0], a.window, a.chunked);
     ti.k_begin = (kb / TK) * TK;
     for (int g = 0; g < GROUPS; ++g) {
       ti.n_tiles[g] = ti.nq[g] > 0 ? (ti.pos0[g] + ti.nq[g] - ti.k_begin + TK - 1) / TK : 0;
@@ -501,12 +501,12 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(const __grid_co
           sv[48 + c] = __uint_as_float(r3_[c]);
         }
       }
-      const bool need_mask = (kt + TK - 1 > pos0 + gw * 32) || (a.window > 0 && kt <= pos0 + gw * 32 + 31 - a.window);
+      const bool need_mask = (kt + TK - 1 > pos0 + gw * 32) || (a.window > 0 && kt < mask_first(pos0 + gw * 32 + 31, a.window, a.chunked));
       if (need_mask) {
 #pragma unroll
         for (int c = 0; c < TK; ++c) {
           const int key = kt + c;
-          const bool valid = key <= qpos && (a.window == 0 || key > qpos - a.window);
+          const bool valid = key <= qpos && key >= mask_first(qpos, a.window, a.chunked);
           sv[c] = valid ? sv[c] : -INFINITY;
         }
       }
@@ -573,7 +573,7 @@ __global__ void __launch_bounds__(384, 1) attn_prefill_tc_kernel(const __grid_co
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (ok && !*abortp) {
       // a sink joins the sum with its own weight 2^(sink - M) and carries no value; a gate scales the head's output
-      if (a.has_sink) l_run += fast_exp2(a.sink_score * LOG2E - m_run);
+      if (a.has_sink) l_run += fast_exp2((a.sinks ? a.sinks[h] : a.sink_score) * LOG2E - m_run);
       float inv = l_run > 0.f ? 1.0f / l_run : 0.f;
       if (a.gate && r < ti.nq[g]) inv *= a.gate[(long long)(q_tok0 + g * BQ + r) * a.nh + h];
       bf16* dst = (bf16*)a.out + ((long long)(q_tok0 + g * BQ + r) * a.nh + h) * HD;

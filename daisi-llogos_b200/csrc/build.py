@@ -37,6 +37,9 @@ SOURCES: Dict[str, List[str]] = {
     "sampling": ["sampling.cu", "common.cuh"],
     "init": ["init.cu", "common.cuh"],
     "block_runner": ["block_runner.cu", "kernel_args.h"],
+    "layernorm": ["layernorm.cu", "common.cuh", "kernel_args.h"],
+    "latent": ["latent.cu", "common.cuh", "kernel_args.h"],
+    "moe": ["moe.cu", "common.cuh", "kernel_args.h"],
 }
 
 NVCC_FLAGS = [

@@ -322,10 +322,13 @@ __global__ void qk_prep_kernel(QkPrepArgs a) {
   if (item >= (long long)a.n_tokens * heads) return;
   const int n = (int)(item / heads);
   const int h = (int)(item % heads);
-  const int hd = a.hd;
-  float* x = sm + warp * hd;
   const int kind = h < a.nh ? 0 : (h < a.nh + a.nkv ? 1 : 2);  // 0 query, 1 key, 2 value
-  const long long off = (long long)n * heads * hd + (long long)h * hd;
+  const int vd = a.vd > 0 ? a.vd : a.hd;
+  const int hd = kind == 2 ? vd : a.hd;                        // elements of this head
+  float* x = sm + warp * max(a.hd, vd);
+  const long long row_w = (long long)(a.nh + a.nkv) * a.hd + (long long)a.nkv * vd;
+  const long long col = kind == 2 ? (long long)(a.nh + a.nkv) * a.hd + (long long)(h - a.nh - a.nkv) * vd : (long long)h * a.hd;
+  const long long off = (long long)n * row_w + col;
   const IT* src = (const IT*)a.qkv + off;
 
   const float rs = row_scale_of(a.row_scale, n);
@@ -344,8 +347,19 @@ __global__ void qk_prep_kernel(QkPrepArgs a) {
     for (int d = lane; d < hd; d += 32) x[d] = x[d] * inv * to_f32(nw[d]);
   }
   if (a.bias) {
-    const WT* b = (const WT*)a.bias + (long long)h * hd;
+    const WT* b = (const WT*)a.bias + col;
     for (int d = lane; d < hd; d += 32) x[d] += to_f32(b[d]);
+  }
+  if (kind == 2 && (a.v_first_out || a.v_first_in)) {
+    // values blended across layers: the first layer of a group lends its values as projected, the others keep
+    // (1 - lam) v + lam v_first; all of it in float32
+    const long long vo = ((long long)n * a.nkv + (h - a.nh - a.nkv)) * vd;
+    if (a.v_first_out)
+      for (int d = lane; d < hd; d += 32) a.v_first_out[vo + d] = x[d];
+    if (a.v_first_in) {
+      const float lam = a.v_mix[0];
+      for (int d = lane; d < hd; d += 32) x[d] = (1.0f - lam) * x[d] + lam * a.v_first_in[vo + d];
+    }
   }
   __syncwarp();
   const int pos = a.positions[n];
@@ -532,7 +546,10 @@ LLG_API int llg_qk_prep(const QkPrepArgs* args, int out_dtype, cudaStream_t stre
   if (a.n_tokens == 0) return 0;
   // the vector kernel moves four elements at a time: every pointer must be 16-byte aligned
   auto aligned = [](const void* p) { return ((uintptr_t)p & 15u) == 0; };
-  const bool lane_ok = (a.hd == 64 || a.hd == 128 || a.hd == 256) &&
+  const bool plain_values = (a.vd == 0 || a.vd == a.hd) && !a.v_first_in && !a.v_first_out;
+  LLG_REQUIRE(a.vd >= 0 && a.vd <= 1024, "qk_prep: value head size %d is larger than 1024", a.vd);
+  LLG_REQUIRE(!a.v_first_in || a.v_mix, "qk_prep: blending values needs the blend's weight");
+  const bool lane_ok = plain_values && (a.hd == 64 || a.hd == 128 || a.hd == 256) &&
                        (!a.cos_table || (a.pairing == 0 && a.rotary_dim == a.hd)) && a.partial_stride % 4 == 0 &&
                        aligned(a.qkv) && aligned(a.q_norm_w) && aligned(a.k_norm_w) && aligned(a.bias) &&
                        aligned(a.cos_table) && aligned(a.sin_table) && aligned(a.q_out) && aligned(a.k_new) &&
@@ -544,7 +561,7 @@ LLG_API int llg_qk_prep(const QkPrepArgs* args, int out_dtype, cudaStream_t stre
   // the vector kernel gives a head to head_dim / 8 lanes, the general one to a warp
   const long long per_block = lane_ok ? (long long)warps * 32 / (a.hd / 8) : warps;
   const unsigned grid = (unsigned)((items + per_block - 1) / per_block);
-  const size_t smem = lane_ok ? 0 : (size_t)warps * a.hd * sizeof(float);
+  const size_t smem = lane_ok ? 0 : (size_t)warps * (a.hd > a.vd ? a.hd : a.vd) * sizeof(float);
   const bool w_bf16 = (a.q_norm_w || a.k_norm_w) ? a.norm_w_dtype == LLG_BF16
                                                  : (a.bias ? a.bias_dtype == LLG_BF16 : false);
   if ((a.q_norm_w || a.k_norm_w) && a.bias)

@@ -16,6 +16,13 @@ struct RowScale {
 };
 
 #ifdef __CUDACC__
+// The first position that a query at position `pos` sees under a mask of size `window` (0: every position): its own
+// chunk's first position, or the first of the last `window` positions.
+__device__ __forceinline__ int mask_first(int pos, int window, int chunked) {
+  if (window <= 0) return 0;
+  return chunked ? (pos / window) * window : max(0, pos - window + 1);
+}
+
 __device__ __forceinline__ float row_scale_of(const RowScale& s, long long row) {
   if (!s.ss) return 1.0f;
   const float* p = s.ss + row * s.parts;
@@ -60,6 +67,13 @@ struct QkPrepArgs {
   const int* slots;
   int n_tokens, nh, nkv, hd;
   RowScale row_scale;         // of the token rows of qkv (applied to the summed partials, before anything else)
+  // Further forms; all zero gives the plain one.  Only the general kernel of elementwise.cu reads these (a caller
+  // leaves them zero for the product whose epilogue is the preparation).
+  int vd;                     // elements of a value head; 0 = hd.  A row of qkv then is nh*hd + nkv*hd + nkv*vd wide,
+                              // and v_new / v_pages hold vd per head
+  const float* v_mix;         // one number lam, or null: with v_first_in the values become (1 - lam) v + lam v_first_in
+  const float* v_first_in;    // [n_tokens][nkv][vd] float32 or null
+  float* v_first_out;         // [n_tokens][nkv][vd] float32 or null: receives the values as projected (before any blend)
 };
 
 // Attention for a step with several tokens per sequence (attention_simt.cu, attention_mma.cu, attention_tc.cu).
@@ -87,6 +101,9 @@ struct PrefillArgs {
   int has_sink;             // 1: a sink of score sink_score joins every softmax's denominator and carries no value
   float sink_score;
   const float* gate;        // [n_tokens][nh] or null: a head's output is multiplied by its token's gate
+  const float* sinks;       // [nh] or null: with has_sink, query head h's sink has the score sinks[h] instead of sink_score
+  int chunked;              // 1: `window` is a chunk size: a query at position p sees the keys from (p / window) * window
+                            // on (its own chunk, counted from position 0) instead of the last `window` keys
 };
 
 // Attention of one new token per sequence, split kernels (attention_simt.cu, attention_mma.cu).
@@ -108,6 +125,8 @@ struct DecodeArgs {
   int has_sink;
   float sink_score;
   const float* gate;        // [B][nh] or null
+  const float* sinks;       // as in PrefillArgs
+  int chunked;
 };
 
 // Attention of one new token per sequence, TMA kernel (attention_decode_tma.cu).
@@ -127,6 +146,8 @@ struct DecodeTmaArgs {
   int has_sink;               // as in PrefillArgs (value heads have the key heads' size here)
   float sink_score;
   const float* gate;          // [n_seqs][nh] or null
+  const float* sinks;         // as in PrefillArgs
+  int chunked;
 };
 
 // Residual kept as several streams (hyper-connections), elementwise.cu: hc_add_rmsnorm.  For output row j (token
@@ -182,4 +203,83 @@ struct QkvRowPrepArgs {
   const int* slots;
   float* gate_out;            // [n_tokens][nh] or null (the row then has no gate part)
   int n_tokens, nh, nkv, hd, vd;
+};
+
+// Layer norm fused with the residual add (layernorm.cu).  For output row j (token r = rows ? rows[j] : j):
+//   v = residual[r] + scale * (sum over all given sets of partials)      (written back when there are any)
+//   out[j] = (v - mean(v)) / sqrt(mean((v - mean(v))^2) + eps) * weight + bias
+// Up to LLG_LN_BRANCHES sets of partials (sublayers that ran side by side on the same norm's output).
+#define LLG_LN_BRANCHES 4
+struct LayerNormArgs {
+  float* residual;            // [n_tokens][hidden]
+  const float* branch[LLG_LN_BRANCHES];   // each [n_partials[i]][n_tokens][hidden] or null
+  int n_partials[LLG_LN_BRANCHES];
+  long long partial_stride;   // elements between partials (n_tokens * hidden)
+  float scale;
+  const void* weight;         // [hidden]
+  const void* bias;           // [hidden]
+  int w_dtype;
+  float eps;
+  void* out;                  // [n_out][hidden]
+  int out_dtype;
+  const int* rows;            // [n_out] or null
+  int n_out, hidden;
+};
+
+// Preparation for latent attention (latent.cu: latent_prep).  A row of the input product holds, per token,
+// nh * (dim + rdim) query elements (head by head: dim unrotated, rdim rotated), then `rank` latent elements, then rdim
+// elements of the key part that all heads share.
+struct LatentPrepArgs {
+  const float* rows;          // [n_partials][n_tokens][nh * (dim + rdim) + rank + rdim]
+  int n_partials;
+  long long partial_stride;
+  const void* c_norm_w;       // [rank]
+  int w_dtype;
+  float norm_eps;
+  const float* cos_table;     // [positions][rdim / 2] or null (rdim == 0)
+  const float* sin_table;
+  int table_positions;
+  const int* positions;       // [n_tokens]
+  void* q_plain;              // [n_tokens][nh][dim]
+  void* q_out;                // [n_tokens][nh][rank + rdim]; only the last rdim of every head are written here
+  void* k_new;                // [n_tokens][1][rank + rdim] or null
+  void* v_new;                // [n_tokens][1][rank] or null
+  void* k_pages;              // paged store or null
+  void* v_pages;
+  const int* page_table;
+  int table_width;
+  int ring_pages;
+  const int* seq_of_token;
+  const int* slots;
+  int n_tokens, nh, dim, rdim, rank;
+};
+
+// y[n][h][o] = sum_k w[h][o][k] x[n][h][k] (latent.cu: head_linear).  x and y may be parts of wider rows: their
+// strides between tokens and between heads are given in elements; the innermost elements are contiguous.
+struct HeadLinearArgs {
+  const void* x;
+  long long x_token_stride, x_head_stride;
+  const void* w;              // [nh][n_out][n_in]
+  void* y;
+  long long y_token_stride, y_head_stride;
+  int n_tokens, nh, n_in, n_out;
+};
+
+// Mixture of experts (moe.cu).  The step's (token, choice) pairs are laid out as rows in the order of their experts, every
+// expert's run filled up to whole tiles of LLG_MOE_TILE rows: row_of_pair[p] is pair p's row, token_of_row[r] the token
+// whose activations row r reads (-1: a filling row), tile_expert[t] the expert of tile t's rows (-1: an unused tile).
+#define LLG_MOE_TILE 32
+#define LLG_MOE_MAX_EXPERTS 1024
+#define LLG_MOE_MAX_TOP 32
+
+// y[r][o] = sum_k w[e][o][k] x[src(r)][k] for every row r of every tile with an expert e; GATED: two matrices per expert
+// and y = silu(w . x) * (w2 . x).
+struct GroupedLinearArgs {
+  const void* x;              // [.][n_in]; row src(r) = token_of_row ? token_of_row[r] : r
+  const int* token_of_row;    // [rows] or null
+  const int* tile_expert;     // [rows / LLG_MOE_TILE]
+  const void* w;              // [experts][n_out][n_in]
+  const void* w2;             // the same shape, or null
+  void* y;                    // [rows][n_out]
+  int rows, n_in, n_out;
 };

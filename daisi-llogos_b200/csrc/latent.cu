@@ -1,0 +1,173 @@
+// Kernels of latent attention (keys and values of all heads from one latent vector per token):
+//
+//   latent_prep : from the rows of the input product [q of all heads | latent | rotated key part] (float32 partial sums):
+//                 the latent is RMS-normed with its weight, the rotated parts of every query head and the shared key part
+//                 are rotated by the token's position (pairs (i, i + rot_dim/2), tables of cos and sin), and the results are
+//                 written as the attention kernels read them: keys [latent | rotated part] and values [latent] for ONE
+//                 key/value head (packed for a prompt step and/or into the cache pages), the queries' rotated parts behind
+//                 the place where head_linear puts the unrotated parts' products, and the unrotated parts by themselves.
+//   head_linear : y[n][h][:] = W_h x[n][h][:], a small product per (token, head) with one matrix per head; float32 sums.
+//
+// Statistics, angles' tables and sums are float32; inputs and outputs float32 or bfloat16.
+#include "common.cuh"
+#include "kernel_args.h"
+
+LLG_API const char* llg_last_error() { return g_llg_error; }
+
+namespace {
+
+// one warp per unit: unit 0 .. nh-1 = a query head, unit nh = latent and shared key part
+template <typename OT, typename WT>
+__global__ void latent_prep_kernel(LatentPrepArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int units = a.nh + 1;
+  const long long item = (long long)blockIdx.x * warps + warp;
+  if (item >= (long long)a.n_tokens * units) return;
+  const int n = (int)(item / units), u = (int)(item % units);
+  const int qd = a.dim + a.rdim, kd = a.rank + a.rdim, half = a.rdim >> 1;
+  const long long row_w = (long long)a.nh * qd + kd;
+  const float* src = a.rows + (long long)n * row_w;
+  const int pos = a.positions[n];
+  const int p = pos < a.table_positions ? pos : a.table_positions - 1;        // bounded; the host checks the tables' reach
+  const float* cs = a.cos_table ? a.cos_table + (long long)p * half : nullptr;
+  const float* sn = a.sin_table ? a.sin_table + (long long)p * half : nullptr;
+  auto summed = [&](long long col) {
+    float v = 0.f;
+    for (int s = 0; s < a.n_partials; ++s) v += src[s * a.partial_stride + col];
+    return v;
+  };
+  if (u < a.nh) {
+    const long long col = (long long)u * qd;
+    OT* qp = (OT*)a.q_plain + ((long long)n * a.nh + u) * a.dim;
+    for (int d = lane; d < a.dim; d += 32) qp[d] = from_f32<OT>(summed(col + d));
+    OT* qo = (OT*)a.q_out + ((long long)n * a.nh + u) * kd + a.rank;
+    for (int i = lane; i < half; i += 32) {
+      const float x0 = summed(col + a.dim + i), x1 = summed(col + a.dim + half + i);
+      qo[i] = from_f32<OT>(x0 * cs[i] - x1 * sn[i]);
+      qo[half + i] = from_f32<OT>(x1 * cs[i] + x0 * sn[i]);
+    }
+    return;
+  }
+  // the latent: RMS norm over its kv_rank elements
+  const long long col = (long long)a.nh * qd;
+  float ss = 0.f;
+  for (int d = lane; d < a.rank; d += 32) {
+    const float v = summed(col + d);
+    ss += v * v;
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)a.rank + a.norm_eps);
+  OT* kn = a.k_new ? (OT*)a.k_new + (long long)n * kd : nullptr;
+  OT* vn = a.v_new ? (OT*)a.v_new + (long long)n * a.rank : nullptr;
+  OT *kp = nullptr, *vp = nullptr;
+  if (a.k_pages) {
+    const int slot = a.slots[a.seq_of_token[n]];
+    const long long r = kv_row(a.page_table, a.table_width, a.ring_pages, slot, pos, 0, 1);
+    kp = (OT*)a.k_pages + r * kd;
+    vp = (OT*)a.v_pages + r * a.rank;
+  }
+  const WT* w = (const WT*)a.c_norm_w;
+  for (int d = lane; d < a.rank; d += 32) {
+    const OT c = from_f32<OT>(summed(col + d) * inv * to_f32(w[d]));
+    if (kn) { kn[d] = c; vn[d] = c; }
+    if (kp) { kp[d] = c; vp[d] = c; }
+  }
+  for (int i = lane; i < half; i += 32) {
+    const float x0 = summed(col + a.rank + i), x1 = summed(col + a.rank + half + i);
+    const OT r0 = from_f32<OT>(x0 * cs[i] - x1 * sn[i]), r1 = from_f32<OT>(x1 * cs[i] + x0 * sn[i]);
+    if (kn) { kn[a.rank + i] = r0; kn[a.rank + half + i] = r1; }
+    if (kp) { kp[a.rank + i] = r0; kp[a.rank + half + i] = r1; }
+  }
+}
+
+// y[n][h][o] = sum_k w[h][o][k] x[n][h][k].  A block takes TN tokens of one head and TO outputs; x's tile lies in shared
+// memory as float32, a thread owns one output column for TN / (threads / TO) tokens... kept simple: thread (to, tn)
+// computes y for output to0 + to and tokens tn, tn + TY, ...; w rows are read once per block through shared memory.
+constexpr int HL_TN = 32, HL_TO = 32, HL_TK = 32;
+
+template <typename XT, typename WT, typename YT>
+__global__ void __launch_bounds__(256) head_linear_kernel(HeadLinearArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float xs[HL_TN][HL_TK + 1];
+  __shared__ float ws[HL_TO][HL_TK + 1];
+  const int h = blockIdx.z;
+  const int n0 = blockIdx.x * HL_TN, o0 = blockIdx.y * HL_TO;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;          // tx: output within the tile, ty: 8 token groups
+  const XT* x = (const XT*)a.x;
+  const WT* w = (const WT*)a.w + (long long)h * a.n_out * a.n_in;
+  float acc[HL_TN / 8];
+#pragma unroll
+  for (int i = 0; i < HL_TN / 8; ++i) acc[i] = 0.f;
+  for (int k0 = 0; k0 < a.n_in; k0 += HL_TK) {
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < HL_TN * HL_TK; idx += 256) {
+      const int r = idx / HL_TK, c = idx % HL_TK;
+      const int n = n0 + r, k = k0 + c;
+      xs[r][c] = (n < a.n_tokens && k < a.n_in) ? to_f32(x[(long long)n * a.x_token_stride + (long long)h * a.x_head_stride + k]) : 0.f;
+    }
+    for (int idx = threadIdx.x; idx < HL_TO * HL_TK; idx += 256) {
+      const int r = idx / HL_TK, c = idx % HL_TK;
+      const int o = o0 + r, k = k0 + c;
+      ws[r][c] = (o < a.n_out && k < a.n_in) ? to_f32(w[(long long)o * a.n_in + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < HL_TK; ++k) {
+      const float wv = ws[tx][k];
+#pragma unroll
+      for (int i = 0; i < HL_TN / 8; ++i) acc[i] = fmaf(xs[ty + 8 * i][k], wv, acc[i]);
+    }
+  }
+  YT* y = (YT*)a.y;
+  const int o = o0 + tx;
+  if (o < a.n_out) {
+#pragma unroll
+    for (int i = 0; i < HL_TN / 8; ++i) {
+      const int n = n0 + ty + 8 * i;
+      if (n < a.n_tokens) y[(long long)n * a.y_token_stride + (long long)h * a.y_head_stride + o] = from_f32<YT>(acc[i]);
+    }
+  }
+}
+
+}  // namespace
+
+LLG_API int llg_latent_prep(const LatentPrepArgs* args, int out_dtype, cudaStream_t stream) {
+  const LatentPrepArgs& a = *args;
+  LLG_REQUIRE(a.n_tokens >= 0 && a.nh > 0 && a.dim > 0 && a.rank > 0 && a.rdim >= 0 && a.rdim % 2 == 0, "latent_prep: bad sizes");
+  LLG_REQUIRE(a.n_partials >= 1, "latent_prep: n_partials must be >= 1");
+  LLG_REQUIRE(a.rdim == 0 || (a.cos_table && a.sin_table && a.table_positions > 0), "latent_prep: rotated elements need the tables");
+  LLG_REQUIRE(!a.k_pages || (a.v_pages && a.page_table && a.slots && a.seq_of_token && a.ring_pages > 0),
+              "latent_prep: a cache write needs both page stores, page_table, slots and seq_of_token");
+  LLG_REQUIRE(!a.k_new == !a.v_new, "latent_prep: packed keys and values come together");
+  if (a.n_tokens == 0) return 0;
+  const int warps = 4;
+  const long long items = (long long)a.n_tokens * (a.nh + 1);
+  const unsigned grid = (unsigned)((items + warps - 1) / warps);
+  const bool wb = a.w_dtype == LLG_BF16;
+  if (out_dtype == LLG_F32) {
+    if (wb) llg_launch(latent_prep_kernel<float, __nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, stream, a);
+    else llg_launch(latent_prep_kernel<float, float>, dim3(grid), dim3(warps * 32), 0, stream, a);
+  } else if (out_dtype == LLG_BF16) {
+    if (wb) llg_launch(latent_prep_kernel<__nv_bfloat16, __nv_bfloat16>, dim3(grid), dim3(warps * 32), 0, stream, a);
+    else llg_launch(latent_prep_kernel<__nv_bfloat16, float>, dim3(grid), dim3(warps * 32), 0, stream, a);
+  } else {
+    return llg_fail("latent_prep: unknown output dtype %d", out_dtype);
+  }
+  return llg_check_launch("latent_prep");
+}
+
+LLG_API int llg_head_linear(const HeadLinearArgs* args, int dtype, cudaStream_t stream) {
+  const HeadLinearArgs& a = *args;
+  LLG_REQUIRE(a.n_tokens >= 0 && a.nh > 0 && a.n_in > 0 && a.n_out > 0, "head_linear: bad sizes");
+  LLG_REQUIRE(a.nh <= 65535, "head_linear: too many heads");
+  if (a.n_tokens == 0) return 0;
+  dim3 grid((a.n_tokens + HL_TN - 1) / HL_TN, (a.n_out + HL_TO - 1) / HL_TO, a.nh);
+  if (dtype == LLG_F32) llg_launch(head_linear_kernel<float, float, float>, grid, dim3(256), 0, stream, a);
+  else if (dtype == LLG_BF16)
+    llg_launch(head_linear_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>, grid, dim3(256), 0, stream, a);
+  else return llg_fail("head_linear: unknown dtype %d", dtype);
+  return llg_check_launch("head_linear");
+}

@@ -1,0 +1,258 @@
+// Mixture of experts: routing, the layout of a step's (token, choice) pairs by expert, the experts' two grouped products
+// on the CUDA cores, and the weighted sum (argument blocks and the layout in kernel_args.h).
+//
+//   moe_route   : z = W_r x + b in float32 (x may be bfloat16), the `top` largest per token (ties: the lower index), weights
+//                 softmax over the chosen z alone.
+//   moe_plan    : one block counts the pairs of every expert, lays the experts' runs out one after another, each filled
+//                 up to whole tiles, and gives every pair its row.  Which row of its expert's run a pair gets depends on
+//                 the order in which the threads arrive; no result depends on it (a row's values come from its own token
+//                 alone, and a token's rows are added in the order of its choices).
+//   grouped products: a block takes one tile of rows (one expert) and 32 outputs.
+//   moe_combine : out[n] = sum_k weight[n][k] y[row of (n, k)] + the shared expert's partial sums.
+#include "common.cuh"
+#include "kernel_args.h"
+
+LLG_API const char* llg_last_error() { return g_llg_error; }
+LLG_API int llg_moe_tile_rows() { return LLG_MOE_TILE; }
+LLG_API int llg_moe_max_experts() { return LLG_MOE_MAX_EXPERTS; }
+LLG_API int llg_moe_max_top() { return LLG_MOE_MAX_TOP; }
+
+namespace {
+
+template <typename XT>
+__global__ void __launch_bounds__(128) moe_route_kernel(const XT* __restrict__ x, const float* __restrict__ w,
+                                                        const float* __restrict__ bias, int* __restrict__ choice,
+                                                        float* __restrict__ weight, int hidden, int n_exp, int top) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  float* xs = sm;                   // [hidden]
+  float* z = sm + hidden;           // [n_exp]
+  __shared__ float chosen[LLG_MOE_MAX_TOP];
+  const int n = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) xs[i] = to_f32(x[(long long)n * hidden + i]);
+  __syncthreads();
+  for (int e = warp; e < n_exp; e += 4) {
+    const float* we = w + (long long)e * hidden;
+    float s = 0.f;
+    for (int i = lane; i < hidden; i += 32) s = fmaf(we[i], xs[i], s);
+    s = warp_sum(s);
+    if (lane == 0) z[e] = s + (bias ? bias[e] : 0.f);
+  }
+  __syncthreads();
+  if (warp != 0) return;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int e = lane; e < n_exp; e += 32) {
+      const float v = z[e];
+      if (v > best) { best = v; arg = e; }          // a lane meets its experts in rising order: the first of equals stays
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+    }
+    if (arg == 0x7fffffff) arg = 0;                 // nothing but -inf or NaN left: still a valid index
+    if (lane == 0) {
+      choice[(long long)n * top + k] = arg;
+      chosen[k] = best;
+      z[arg] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  // softmax over the chosen logits; the first chosen is the largest
+  const float m = chosen[0];
+  float ev = lane < top ? expf(chosen[lane] - m) : 0.f;
+  const float total = warp_sum(ev);
+  if (lane < top) weight[(long long)n * top + lane] = ev / total;
+}
+
+__global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ choice, int n_pairs, int top, int n_exp,
+                                                        int* __restrict__ row_of_pair, int* __restrict__ token_of_row,
+                                                        int* __restrict__ tile_expert, int cap) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ int counts[LLG_MOE_MAX_EXPERTS], starts[LLG_MOE_MAX_EXPERTS], cursor[LLG_MOE_MAX_EXPERTS];
+  const int tid = threadIdx.x, nt = blockDim.x;
+  for (int e = tid; e < n_exp; e += nt) counts[e] = cursor[e] = 0;
+  for (int r = tid; r < cap; r += nt) token_of_row[r] = -1;
+  for (int t = tid; t < cap / LLG_MOE_TILE; t += nt) tile_expert[t] = -1;
+  __syncthreads();
+  for (int p = tid; p < n_pairs; p += nt) {
+    const int e = choice[p];
+    if (e >= 0 && e < n_exp) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int at = 0;
+    for (int e = 0; e < n_exp; ++e) {
+      starts[e] = at;
+      at += (counts[e] + LLG_MOE_TILE - 1) / LLG_MOE_TILE * LLG_MOE_TILE;
+    }
+  }
+  __syncthreads();
+  for (int e = tid; e < n_exp; e += nt) {
+    const int t0 = starts[e] / LLG_MOE_TILE, t1 = t0 + (counts[e] + LLG_MOE_TILE - 1) / LLG_MOE_TILE;
+    for (int t = t0; t < t1; ++t) tile_expert[t] = e;
+  }
+  for (int p = tid; p < n_pairs; p += nt) {
+    const int e = choice[p];
+    int row = 0;
+    if (e >= 0 && e < n_exp) {
+      row = starts[e] + atomicAdd(&cursor[e], 1);
+      token_of_row[row] = p / top;
+    }
+    row_of_pair[p] = row;
+  }
+}
+
+constexpr int GT_O = 32, GT_K = 32;
+
+template <typename XT, typename WT, typename YT, bool GATED>
+__global__ void __launch_bounds__(256) grouped_linear_kernel(GroupedLinearArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float xs[LLG_MOE_TILE][GT_K + 1];
+  __shared__ float ws[GT_O][GT_K + 1];
+  __shared__ float ws2[GATED ? GT_O : 1][GT_K + 1];
+  __shared__ int src[LLG_MOE_TILE];
+  const int tile = blockIdx.x;
+  const int e = a.tile_expert[tile];
+  if (e < 0) return;
+  const int r0 = tile * LLG_MOE_TILE, o0 = blockIdx.y * GT_O;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  if (threadIdx.x < LLG_MOE_TILE) src[threadIdx.x] = a.token_of_row ? a.token_of_row[r0 + threadIdx.x] : r0 + threadIdx.x;
+  const XT* x = (const XT*)a.x;
+  const WT* w = (const WT*)a.w + (long long)e * a.n_out * a.n_in;
+  const WT* w2 = GATED ? (const WT*)a.w2 + (long long)e * a.n_out * a.n_in : nullptr;
+  constexpr int RPT = LLG_MOE_TILE / 8;             // rows per thread
+  float acc[RPT], acc2[RPT];
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) acc[i] = acc2[i] = 0.f;
+  for (int k0 = 0; k0 < a.n_in; k0 += GT_K) {
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < LLG_MOE_TILE * GT_K; idx += 256) {
+      const int r = idx / GT_K, c = idx % GT_K;
+      const int s = src[r], k = k0 + c;
+      xs[r][c] = (s >= 0 && k < a.n_in) ? to_f32(x[(long long)s * a.n_in + k]) : 0.f;
+    }
+    for (int idx = threadIdx.x; idx < GT_O * GT_K; idx += 256) {
+      const int r = idx / GT_K, c = idx % GT_K;
+      const int o = o0 + r, k = k0 + c;
+      const bool in = o < a.n_out && k < a.n_in;
+      ws[r][c] = in ? to_f32(w[(long long)o * a.n_in + k]) : 0.f;
+      if (GATED) ws2[r][c] = in ? to_f32(w2[(long long)o * a.n_in + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < GT_K; ++k) {
+      const float wv = ws[tx][k];
+      const float wv2 = GATED ? ws2[tx][k] : 0.f;
+#pragma unroll
+      for (int i = 0; i < RPT; ++i) {
+        const float xv = xs[ty + 8 * i][k];
+        acc[i] = fmaf(xv, wv, acc[i]);
+        if (GATED) acc2[i] = fmaf(xv, wv2, acc2[i]);
+      }
+    }
+  }
+  const int o = o0 + tx;
+  if (o >= a.n_out) return;
+  YT* y = (YT*)a.y;
+#pragma unroll
+  for (int i = 0; i < RPT; ++i) {
+    const int r = r0 + ty + 8 * i;
+    float v = acc[i];
+    if (GATED) v = v / (1.0f + expf(-v)) * acc2[i];
+    y[(long long)r * a.n_out + o] = from_f32<YT>(v);         // filling rows hold zeros
+  }
+}
+
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ row_of_pair,
+                                   const float* __restrict__ weight, const float* __restrict__ shared, int n_shared,
+                                   long long shared_stride, float* __restrict__ out, int hidden, int top) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n = blockIdx.x;
+  for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
+    float v = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int row = row_of_pair[(long long)n * top + k];
+      v = fmaf(weight[(long long)n * top + k], y[(long long)row * hidden + d], v);
+    }
+    for (int s = 0; s < n_shared; ++s) v += shared[s * shared_stride + (long long)n * hidden + d];
+    out[(long long)n * hidden + d] = v;
+  }
+}
+
+}  // namespace
+
+LLG_API int llg_moe_route(const void* x, int x_dtype, const float* w, const float* bias, int* choice, float* weight,
+                          int n_tokens, int hidden, int n_exp, int top, cudaStream_t stream) {
+  LLG_REQUIRE(n_tokens >= 0 && hidden > 0, "moe_route: bad sizes");
+  LLG_REQUIRE(n_exp > 0 && n_exp <= LLG_MOE_MAX_EXPERTS, "moe_route: %d experts are outside [1, %d]", n_exp, LLG_MOE_MAX_EXPERTS);
+  LLG_REQUIRE(top > 0 && top <= n_exp && top <= LLG_MOE_MAX_TOP, "moe_route: top %d of %d experts (at most %d)", top, n_exp,
+              LLG_MOE_MAX_TOP);
+  if (n_tokens == 0) return 0;
+  const size_t smem = (size_t)(hidden + n_exp) * sizeof(float);
+  LLG_REQUIRE(smem <= 200 * 1024, "moe_route: rows of %d elements do not fit shared memory", hidden);
+  if (x_dtype == LLG_F32) {
+    if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    llg_launch(moe_route_kernel<float>, dim3(n_tokens), dim3(128), smem, stream, (const float*)x, w, bias, choice, weight, hidden,
+               n_exp, top);
+  } else if (x_dtype == LLG_BF16) {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    llg_launch(moe_route_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), smem, stream, (const __nv_bfloat16*)x, w, bias, choice,
+               weight, hidden, n_exp, top);
+  } else {
+    return llg_fail("moe_route: unknown dtype %d", x_dtype);
+  }
+  return llg_check_launch("moe_route");
+}
+
+LLG_API int llg_moe_plan(const int* choice, int n_pairs, int top, int n_exp, int* row_of_pair, int* token_of_row,
+                         int* tile_expert, int cap, cudaStream_t stream) {
+  LLG_REQUIRE(n_exp > 0 && n_exp <= LLG_MOE_MAX_EXPERTS, "moe_plan: %d experts are outside [1, %d]", n_exp, LLG_MOE_MAX_EXPERTS);
+  LLG_REQUIRE(top > 0 && n_pairs >= 0 && n_pairs % top == 0, "moe_plan: %d pairs, top %d", n_pairs, top);
+  const long long need = ((long long)n_pairs + (long long)n_exp * (LLG_MOE_TILE - 1) + LLG_MOE_TILE - 1) / LLG_MOE_TILE * LLG_MOE_TILE;
+  LLG_REQUIRE(cap % LLG_MOE_TILE == 0 && cap >= need, "moe_plan: %d rows, %lld needed (whole tiles)", cap, need);
+  if (n_pairs == 0) return 0;
+  llg_launch(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, choice, n_pairs, top, n_exp, row_of_pair, token_of_row, tile_expert, cap);
+  return llg_check_launch("moe_plan");
+}
+
+LLG_API int llg_grouped_linear(const GroupedLinearArgs* args, int x_dtype, int y_dtype, cudaStream_t stream) {
+  const GroupedLinearArgs& a = *args;
+  LLG_REQUIRE(a.rows >= 0 && a.rows % LLG_MOE_TILE == 0 && a.n_in > 0 && a.n_out > 0, "grouped_linear: bad sizes");
+  if (a.rows == 0) return 0;
+  dim3 grid(a.rows / LLG_MOE_TILE, (a.n_out + GT_O - 1) / GT_O);
+  LLG_REQUIRE(grid.y <= 65535, "grouped_linear: too many outputs");
+  const bool gated = a.w2 != nullptr;
+  if (x_dtype == LLG_F32 && y_dtype == LLG_F32) {
+    if (gated) llg_launch(grouped_linear_kernel<float, float, float, true>, grid, dim3(256), 0, stream, a);
+    else llg_launch(grouped_linear_kernel<float, float, float, false>, grid, dim3(256), 0, stream, a);
+  } else if (x_dtype == LLG_BF16 && y_dtype == LLG_BF16) {
+    if (gated) llg_launch(grouped_linear_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16, true>, grid, dim3(256), 0, stream, a);
+    else llg_launch(grouped_linear_kernel<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16, false>, grid, dim3(256), 0, stream, a);
+  } else if (x_dtype == LLG_BF16 && y_dtype == LLG_F32) {
+    if (gated) llg_launch(grouped_linear_kernel<__nv_bfloat16, __nv_bfloat16, float, true>, grid, dim3(256), 0, stream, a);
+    else llg_launch(grouped_linear_kernel<__nv_bfloat16, __nv_bfloat16, float, false>, grid, dim3(256), 0, stream, a);
+  } else {
+    return llg_fail("grouped_linear: unsupported dtypes x=%d y=%d", x_dtype, y_dtype);
+  }
+  return llg_check_launch("grouped_linear");
+}
+
+LLG_API int llg_moe_combine(const float* y, const int* row_of_pair, const float* weight, const float* shared, int n_shared,
+                            long long shared_stride, float* out, int n_tokens, int hidden, int top, cudaStream_t stream) {
+  LLG_REQUIRE(n_tokens >= 0 && hidden > 0 && top > 0, "moe_combine: bad sizes");
+  LLG_REQUIRE(!shared || n_shared >= 1, "moe_combine: a shared expert's partials need at least one");
+  if (n_tokens == 0) return 0;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  llg_launch(moe_combine_kernel, dim3(n_tokens), dim3(threads), 0, stream, y, row_of_pair, weight, shared, shared ? n_shared : 0,
+             shared_stride, out, hidden, top);
+  return llg_check_launch("moe_combine");
+}

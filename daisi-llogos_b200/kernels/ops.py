@@ -124,6 +124,7 @@ class _QkPrepArgs(Structure):
         ("seq_of_token", c_void_p), ("slots", c_void_p),
         ("n_tokens", c_int), ("nh", c_int), ("nkv", c_int), ("hd", c_int),
         ("row_scale", _RowScale),
+        ("vd", c_int), ("v_mix", c_void_p), ("v_first_in", c_void_p), ("v_first_out", c_void_p),
     ]
 
 
@@ -136,6 +137,7 @@ class _PrefillArgs(Structure):
         ("n_tiles", c_int), ("nh", c_int), ("nkv", c_int), ("hd", c_int),
         ("scale", c_float), ("window", c_int), ("n_tokens", c_int), ("n_pages", c_int),
         ("vd", c_int), ("has_sink", c_int), ("sink_score", c_float), ("gate", c_void_p),
+        ("sinks", c_void_p), ("chunked", c_int),
     ]
 
 
@@ -147,6 +149,7 @@ class _DecodeArgs(Structure):
         ("n_seqs", c_int), ("nh", c_int), ("nkv", c_int), ("hd", c_int), ("n_splits", c_int),
         ("scale", c_float), ("window", c_int),
         ("vd", c_int), ("has_sink", c_int), ("sink_score", c_float), ("gate", c_void_p),
+        ("sinks", c_void_p), ("chunked", c_int),
     ]
 
 
@@ -177,6 +180,45 @@ class _DecodeTmaArgs(Structure):
         ("slots", c_void_p), ("len_before", c_void_p), ("part", c_void_p), ("counters", c_void_p), ("out", c_void_p),
         ("n_seqs", c_int), ("nh", c_int), ("nkv", c_int), ("hd", c_int), ("scale", c_float), ("window", c_int),
         ("has_sink", c_int), ("sink_score", c_float), ("gate", c_void_p),
+        ("sinks", c_void_p), ("chunked", c_int),
+    ]
+
+
+_LN_BRANCHES = 4
+
+
+class _LayerNormArgs(Structure):
+    _fields_ = [
+        ("residual", c_void_p), ("branch", c_void_p * _LN_BRANCHES), ("n_partials", c_int * _LN_BRANCHES),
+        ("partial_stride", c_longlong), ("scale", c_float), ("weight", c_void_p), ("bias", c_void_p), ("w_dtype", c_int),
+        ("eps", c_float), ("out", c_void_p), ("out_dtype", c_int), ("rows", c_void_p), ("n_out", c_int), ("hidden", c_int),
+    ]
+
+
+class _LatentPrepArgs(Structure):
+    _fields_ = [
+        ("rows", c_void_p), ("n_partials", c_int), ("partial_stride", c_longlong),
+        ("c_norm_w", c_void_p), ("w_dtype", c_int), ("norm_eps", c_float),
+        ("cos_table", c_void_p), ("sin_table", c_void_p), ("table_positions", c_int), ("positions", c_void_p),
+        ("q_plain", c_void_p), ("q_out", c_void_p), ("k_new", c_void_p), ("v_new", c_void_p),
+        ("k_pages", c_void_p), ("v_pages", c_void_p), ("page_table", c_void_p), ("table_width", c_int),
+        ("ring_pages", c_int), ("seq_of_token", c_void_p), ("slots", c_void_p),
+        ("n_tokens", c_int), ("nh", c_int), ("dim", c_int), ("rdim", c_int), ("rank", c_int),
+    ]
+
+
+class _HeadLinearArgs(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("x_token_stride", c_longlong), ("x_head_stride", c_longlong), ("w", c_void_p),
+        ("y", c_void_p), ("y_token_stride", c_longlong), ("y_head_stride", c_longlong),
+        ("n_tokens", c_int), ("nh", c_int), ("n_in", c_int), ("n_out", c_int),
+    ]
+
+
+class _GroupedLinearArgs(Structure):
+    _fields_ = [
+        ("x", c_void_p), ("token_of_row", c_void_p), ("tile_expert", c_void_p), ("w", c_void_p), ("w2", c_void_p),
+        ("y", c_void_p), ("rows", c_int), ("n_in", c_int), ("n_out", c_int),
     ]
 
 
@@ -263,6 +305,17 @@ def _load_lib(name: str):
         lib.llg_attn_decode_tma_scratch_floats.restype = c_longlong
         lib.llg_attn_decode_tma.argtypes = [POINTER(_DecodeTmaArgs), c_void_p, c_void_p, c_int, c_int, c_void_p]
         lib.llg_attn_decode_tma_status.restype = c_int
+    elif name == "layernorm":
+        lib.llg_add_layernorm.argtypes = [POINTER(_LayerNormArgs), c_void_p]
+    elif name == "latent":
+        lib.llg_latent_prep.argtypes = [POINTER(_LatentPrepArgs), c_int, c_void_p]
+        lib.llg_head_linear.argtypes = [POINTER(_HeadLinearArgs), c_int, c_void_p]
+    elif name == "moe":
+        lib.llg_moe_route.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        lib.llg_moe_plan.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+        lib.llg_grouped_linear.argtypes = [POINTER(_GroupedLinearArgs), c_int, c_int, c_void_p]
+        lib.llg_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_int,
+                                        c_int, c_void_p]
     elif name == "init":
         lib.llg_fill_normal.argtypes = [c_void_p, c_int, c_longlong, c_ulonglong, ctypes.c_double, ctypes.c_double, c_void_p]
         lib.llg_fill.argtypes = [c_void_p, c_int, c_longlong, c_float, c_void_p]
@@ -440,20 +493,32 @@ def qk_prep(qkv: torch.Tensor, *, n_heads: int, n_kv_heads: int, head_dim: int,
             k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
             page_table: Optional[torch.Tensor] = None, ring_pages: int = 0,
             seq_of_token: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None,
-            row_scale: Optional[RowScale] = None) -> None:
+            row_scale: Optional[RowScale] = None, value_dim: int = 0, v_mix: Optional[torch.Tensor] = None,
+            v_first_in: Optional[torch.Tensor] = None, v_first_out: Optional[torch.Tensor] = None) -> None:
     """Per-head norm (optional), bias (optional), rotation, and the writes of q, k, v.
 
-    ``qkv`` is ``[S, N, (nh + 2 nkv) * hd]`` (partials are summed).  Queries go to ``q_out``;
-    keys and values go to ``k_new``/``v_new`` (packed, for a prompt step) and/or straight into
+    ``qkv`` is ``[S, N, (nh + nkv) * hd + nkv * vd]`` (partials are summed; ``vd = value_dim or hd``).  Queries go to
+    ``q_out``; keys and values go to ``k_new``/``v_new`` (packed, for a prompt step) and/or straight into
     the cache pages (for a one-token step).  ``row_scale``: what a norm left for the token rows; the summed
-    partials are multiplied by it before anything else.
+    partials are multiplied by it before anything else.  Values blended across layers: ``v_first_out`` (float32
+    ``[N, nkv, vd]``) receives the values as projected; with ``v_first_in`` and ``v_mix`` (one float32 number lam on the
+    device) the values written are ``(1 - lam) v + lam v_first_in``.
     """
     lib = _lib("elementwise")
     s, n, width = qkv.shape
-    assert width == (n_heads + 2 * n_kv_heads) * head_dim
+    vd = value_dim or head_dim
+    assert width == (n_heads + n_kv_heads) * head_dim + n_kv_heads * vd
     a = _prep_args(n, n_heads, n_kv_heads, head_dim, q_norm_w, k_norm_w, norm_eps, bias, cos, sin, rotary_dim, pairing,
                    positions, q_out, k_new, v_new, k_pages, v_pages, page_table, ring_pages, seq_of_token, slots)
     a.qkv, a.qkv_dtype, a.n_partials, a.partial_stride = _ptr(qkv), _dt(qkv), s, n * width
+    a.vd = 0 if vd == head_dim else vd
+    for t in (v_first_in, v_first_out):
+        if t is not None and tuple(t.shape) != (n, n_kv_heads, vd):
+            raise KernelError(f"qk_prep: lent values of shape {tuple(t.shape)}, expected {(n, n_kv_heads, vd)}")
+    if (v_first_in is None) != (v_mix is None):
+        raise KernelError("qk_prep: the values to blend with and the blend's weight come together")
+    a.v_mix, a.v_first_in = _ptr(v_mix, torch.float32), _ptr(v_first_in, torch.float32)
+    a.v_first_out = _ptr(v_first_out, torch.float32)
     _set_scale(a, row_scale, n)
     _check(lib, lib.llg_qk_prep(byref(a), _dt(q_out), _stream()))
 
@@ -598,6 +663,183 @@ def qkv_row_prep(qkvg: torch.Tensor, *, n_heads: int, n_kv_heads: int, head_dim:
     _check(lib, lib.llg_qkv_row_prep(byref(a), _dt(q_out), _stream()))
 
 
+def add_layernorm(residual: torch.Tensor, parts, scale: float, weight: torch.Tensor, bias: torch.Tensor, eps: float,
+                  out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """residual += scale * (sum of every set of partials in ``parts``); out[j] = layer norm of residual[rows[j] or j]:
+    ``(v - mean) / sqrt(mean((v - mean)^2) + eps) * weight + bias``.  ``residual`` float32 ``[N, H]``; ``parts`` a sequence
+    of float32 ``[S_i, N, H]`` tensors (up to four; none: nothing is added)."""
+    lib = _lib("layernorm")
+    n, hidden = residual.shape
+    m = out.shape[0]
+    assert out.shape[1] == hidden and weight.shape == (hidden,) and bias.shape == (hidden,)
+    assert rows.numel() == m if rows is not None else m == n
+    if len(parts) > _LN_BRANCHES:
+        raise KernelError(f"add_layernorm: {len(parts)} sets of partials, at most {_LN_BRANCHES}")
+    if weight.dtype != bias.dtype:
+        raise KernelError("add_layernorm: weight and bias must share a dtype")
+    a = _LayerNormArgs()
+    a.residual = _ptr(residual, torch.float32)
+    for i, p in enumerate(parts):
+        assert p.dim() == 3 and p.shape[1:] == (n, hidden), (p.shape, residual.shape)
+        a.branch[i], a.n_partials[i] = _ptr(p, torch.float32), p.shape[0]
+    a.partial_stride, a.scale = n * hidden, float(scale)
+    a.weight, a.bias, a.w_dtype, a.eps = _ptr(weight), _ptr(bias), _dt(weight), float(eps)
+    a.out, a.out_dtype, a.rows, a.n_out, a.hidden = _ptr(out), _dt(out), _ptr(rows, torch.int32), m, hidden
+    _check(lib, lib.llg_add_layernorm(byref(a), _stream()))
+
+
+def latent_prep(rows: torch.Tensor, *, n_heads: int, head_dim: int, rot_dim: int, kv_rank: int, c_norm_w: torch.Tensor,
+                norm_eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], positions: torch.Tensor,
+                q_plain_out: torch.Tensor, q_out: torch.Tensor,
+                k_new: Optional[torch.Tensor] = None, v_new: Optional[torch.Tensor] = None,
+                k_pages: Optional[torch.Tensor] = None, v_pages: Optional[torch.Tensor] = None,
+                page_table: Optional[torch.Tensor] = None, ring_pages: int = 0,
+                seq_of_token: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None) -> None:
+    """Preparation for latent attention from the rows of one product, float32 partials ``[P, N, nh (dim + rdim) + rank +
+    rdim]``: the latent (``rank`` elements, RMS-normed with ``c_norm_w``) and the rotated shared key part become the
+    token's key ``[rank + rdim]`` and value ``[rank]`` of ONE key/value head (packed and/or into the cache pages); every
+    query head's unrotated part goes to ``q_plain_out`` ``[N, nh, dim]`` and its rotated part, rotated, to the last
+    ``rdim`` elements of ``q_out`` ``[N, nh, rank + rdim]`` (the first ``rank`` are ``head_linear``'s to fill)."""
+    lib = _lib("latent")
+    p_n, n, width = rows.shape
+    kd = kv_rank + rot_dim
+    assert width == n_heads * (head_dim + rot_dim) + kd, (width, n_heads, head_dim, rot_dim, kv_rank)
+    assert q_plain_out.shape == (n, n_heads, head_dim) and q_out.shape == (n, n_heads, kd)
+    for t in (q_plain_out, k_new, v_new, k_pages, v_pages):
+        if t is not None and t.dtype != q_out.dtype:
+            raise KernelError("latent_prep: all outputs must share one dtype")
+    a = _LatentPrepArgs()
+    a.rows, a.n_partials, a.partial_stride = _ptr(rows, torch.float32), p_n, n * width
+    a.c_norm_w, a.w_dtype, a.norm_eps = _ptr(c_norm_w), _dt(c_norm_w), float(norm_eps)
+    if rot_dim:
+        assert cos is not None and cos.shape == sin.shape and cos.shape[1] * 2 == rot_dim
+        a.cos_table, a.sin_table, a.table_positions = _ptr(cos, torch.float32), _ptr(sin, torch.float32), cos.shape[0]
+    a.positions = _ptr(positions, torch.int32)
+    a.q_plain, a.q_out, a.k_new, a.v_new = _ptr(q_plain_out), _ptr(q_out), _ptr(k_new), _ptr(v_new)
+    a.k_pages, a.v_pages = _ptr(k_pages), _ptr(v_pages)
+    if k_pages is not None:
+        assert k_pages.shape[1] == 1 and k_pages.shape[3] == kd and v_pages.shape[3] == kv_rank
+    if page_table is not None:
+        a.page_table, a.table_width = _ptr(page_table, torch.int32), page_table.shape[1]
+    a.ring_pages = ring_pages
+    a.seq_of_token, a.slots = _ptr(seq_of_token, torch.int32), _ptr(slots, torch.int32)
+    a.n_tokens, a.nh, a.dim, a.rdim, a.rank = n, n_heads, head_dim, rot_dim, kv_rank
+    _check(lib, lib.llg_latent_prep(byref(a), _dt(q_out), _stream()))
+
+
+def head_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
+    """y[n, h, :] = w[h] x[n, h, :]: ``x`` ``[N, nh, a]``, ``w`` ``[nh, b, a]`` (contiguous), ``y`` ``[N, nh, b]``.  ``x`` and
+    ``y`` may be views into wider rows (their last elements contiguous); float32 sums, one dtype for all three."""
+    lib = _lib("latent")
+    n, nh, k = x.shape
+    assert w.shape[0] == nh and w.shape[2] == k and y.shape == (n, nh, w.shape[1]), (x.shape, w.shape, y.shape)
+    if not (x.is_cuda and w.is_cuda and y.is_cuda):
+        raise KernelError("a kernel was given a tensor that is not on the GPU; there is no CPU path")
+    if x.dtype != w.dtype or x.dtype != y.dtype:
+        raise KernelError("head_linear: x, w and y must share a dtype")
+    if n and (x.stride(2) != 1 or y.stride(2) != 1):
+        raise KernelError("head_linear: the innermost elements of x and y must be contiguous")
+    a = _HeadLinearArgs()
+    a.x, a.x_token_stride, a.x_head_stride = x.data_ptr(), x.stride(0), x.stride(1)
+    a.w = _ptr(w)
+    a.y, a.y_token_stride, a.y_head_stride = y.data_ptr(), y.stride(0), y.stride(1)
+    a.n_tokens, a.nh, a.n_in, a.n_out = n, nh, k, w.shape[1]
+    _check(lib, lib.llg_head_linear(byref(a), _dt(x), _stream()))
+
+
+MOE_TILE_ROWS = 32          # rows of a tile of the experts' grouped products; checked against the library at first use
+MOE_MAX_EXPERTS = 1024
+MOE_MAX_TOP = 32
+
+
+def _moe_lib():
+    lib = _lib("moe")
+    got = (lib.llg_moe_tile_rows(), lib.llg_moe_max_experts(), lib.llg_moe_max_top())
+    if got != (MOE_TILE_ROWS, MOE_MAX_EXPERTS, MOE_MAX_TOP):
+        raise KernelError(f"the mixture-of-experts kernels use (tile, experts, top) = {got}, Python expects "
+                          f"{(MOE_TILE_ROWS, MOE_MAX_EXPERTS, MOE_MAX_TOP)}")
+    return lib
+
+
+def moe_row_capacity(pairs: int, n_experts: int) -> int:
+    """Rows that the (token, choice) pairs of a step can take once every expert's run is filled up to whole tiles."""
+    cap = pairs + n_experts * (MOE_TILE_ROWS - 1)
+    return -(-cap // MOE_TILE_ROWS) * MOE_TILE_ROWS
+
+
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, b_router: Optional[torch.Tensor], choice: torch.Tensor,
+              weight: torch.Tensor) -> None:
+    """Per token: ``z = w_router x + b_router`` in float32, ``choice[n]`` the ``top`` experts of largest z (largest
+    first; of equals the lower index), ``weight[n]`` the softmax over those z.  ``w_router`` and ``b_router`` float32."""
+    lib = _moe_lib()
+    n, hidden = x.shape
+    n_exp, top = w_router.shape[0], choice.shape[1]
+    assert w_router.shape == (n_exp, hidden) and choice.shape == (n, top) and weight.shape == (n, top)
+    assert b_router is None or b_router.shape == (n_exp,)
+    _check(lib, lib.llg_moe_route(_ptr(x), _dt(x), _ptr(w_router, torch.float32), _ptr(b_router, torch.float32),
+                                  _ptr(choice, torch.int32), _ptr(weight, torch.float32), n, hidden, n_exp, top, _stream()))
+
+
+def moe_plan(choice: torch.Tensor, n_experts: int, row_of_pair: torch.Tensor, token_of_row: torch.Tensor,
+             tile_expert: torch.Tensor) -> None:
+    """Lays the pairs ``(n, k)`` of ``choice`` ``[N, top]`` out as rows in the order of their experts, every expert's run
+    filled up to whole tiles of ``MOE_TILE_ROWS``: ``row_of_pair[n * top + k]`` the pair's row, ``token_of_row[r]`` the
+    row's token (-1: a filling row), ``tile_expert[t]`` the expert of tile t (-1: unused).  ``token_of_row`` has
+    ``moe_row_capacity(N * top, n_experts)`` entries."""
+    lib = _moe_lib()
+    n, top = choice.shape
+    cap = token_of_row.numel()
+    assert row_of_pair.numel() == n * top and tile_expert.numel() * MOE_TILE_ROWS == cap
+    _check(lib, lib.llg_moe_plan(_ptr(choice, torch.int32), n * top, top, n_experts, _ptr(row_of_pair, torch.int32),
+                                 _ptr(token_of_row, torch.int32), _ptr(tile_expert, torch.int32), cap, _stream()))
+
+
+def _grouped(x, token_of_row, tile_expert, w, w2, y) -> None:
+    lib = _moe_lib()
+    rows, n_out = y.shape
+    n_in = x.shape[1]
+    assert w.dim() == 3 and w.shape[1:] == (n_out, n_in) and (w2 is None or w2.shape == w.shape)
+    assert tile_expert.numel() * MOE_TILE_ROWS == rows and (token_of_row is None or token_of_row.numel() == rows)
+    assert token_of_row is not None or x.shape[0] == rows
+    if x.dtype != w.dtype or (w2 is not None and w2.dtype != w.dtype):
+        raise KernelError("grouped products: activations and matrices must share a dtype")
+    a = _GroupedLinearArgs()
+    a.x, a.token_of_row, a.tile_expert = _ptr(x), _ptr(token_of_row, torch.int32), _ptr(tile_expert, torch.int32)
+    a.w, a.w2, a.y = _ptr(w), _ptr(w2), _ptr(y)
+    a.rows, a.n_in, a.n_out = rows, n_in, n_out
+    _check(lib, lib.llg_grouped_linear(byref(a), _dt(x), _dt(y), _stream()))
+
+
+def moe_gated(x: torch.Tensor, token_of_row: torch.Tensor, tile_expert: torch.Tensor, w_gate: torch.Tensor,
+              w_up: torch.Tensor, act: torch.Tensor) -> None:
+    """act[r] = silu(w_gate[e] x[t]) * (w_up[e] x[t]) for every row r of the layout (t its token, e its tile's expert);
+    filling rows of a used tile get zeros.  ``w_gate``, ``w_up`` ``[E, inner, hidden]``; ``act`` ``[rows, inner]``."""
+    _grouped(x, token_of_row, tile_expert, w_gate, w_up, act)
+
+
+def moe_down(act: torch.Tensor, tile_expert: torch.Tensor, w_down: torch.Tensor, y: torch.Tensor) -> None:
+    """y[r] = w_down[e] act[r] in float32 for the rows of used tiles.  ``w_down`` ``[E, hidden, inner]``."""
+    if y.dtype != torch.float32:
+        raise KernelError("moe_down: the experts' outputs are float32")
+    _grouped(act, None, tile_expert, w_down, None, y)
+
+
+def moe_combine(y: torch.Tensor, row_of_pair: torch.Tensor, weight: torch.Tensor, shared: Optional[torch.Tensor],
+                out: torch.Tensor) -> None:
+    """out[n] = sum_k weight[n, k] y[row_of_pair[n * top + k]] + the sum of ``shared``'s partials ``[S, N, H]`` (if any)."""
+    lib = _moe_lib()
+    n, top = weight.shape
+    hidden = y.shape[1]
+    assert out.shape == (n, hidden) and row_of_pair.numel() == n * top
+    n_shared = 0
+    if shared is not None:
+        assert shared.dim() == 3 and shared.shape[1:] == (n, hidden)
+        n_shared = shared.shape[0]
+    _check(lib, lib.llg_moe_combine(_ptr(y, torch.float32), _ptr(row_of_pair, torch.int32), _ptr(weight, torch.float32),
+                                    _ptr(shared, torch.float32), n_shared, n * hidden, _ptr(out, torch.float32), n, hidden,
+                                    top, _stream()))
+
+
 ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
 
 
@@ -686,13 +928,21 @@ class AttentionForm:
     """What an attention computes beyond the plain causal softmax over keys and values of one head size:
     ``value_dim`` (elements of a value head; 0 = the key heads' size), ``sink`` (None, or the score of a sink that
     joins every softmax's denominator and carries no value: ``p_j = e^{s_j} / (e^{sink} + sum e^{s_j})``), ``gated``
-    (the output of every (token, head) is multiplied by a float32 gate ``[N, nh]`` that the caller passes)."""
+    (the output of every (token, head) is multiplied by a float32 gate ``[N, nh]`` that the caller passes), ``sinks``
+    (a float32 tensor ``[nh]`` on the device: a sink per query head, instead of one score for all), ``chunked`` (the
+    ``window`` of the call is a chunk size: a query sees the keys of its own chunk of that many positions, chunks
+    counted from position 0, instead of the last ``window`` keys)."""
 
-    def __init__(self, value_dim: int = 0, sink: Optional[float] = None, gated: bool = False):
+    def __init__(self, value_dim: int = 0, sink: Optional[float] = None, gated: bool = False,
+                 sinks: Optional[torch.Tensor] = None, chunked: bool = False):
         self.value_dim, self.sink, self.gated = int(value_dim), (None if sink is None else float(sink)), bool(gated)
+        if sinks is not None and (sinks.dtype != torch.float32 or sinks.dim() != 1):
+            raise KernelError("AttentionForm: per-head sinks are a float32 vector [query heads]")
+        self.sinks, self.chunked = sinks, bool(chunked)
 
     def plain(self, head_dim: int) -> bool:
-        return self.value_dim in (0, head_dim) and self.sink is None and not self.gated
+        return (self.value_dim in (0, head_dim) and self.sink is None and self.sinks is None and not self.gated
+                and not self.chunked)
 
     def one_head_size(self, head_dim: int) -> bool:
         """Keys and values of one head size: what the tensor-core kernels take (sink and gate they all apply)."""
@@ -721,8 +971,17 @@ def prefill_tile_queries(dtype: torch.dtype, head_dim: int, form: AttentionForm 
 def _set_form(a, form: AttentionForm, head_dim: int, gate: Optional[torch.Tensor]) -> None:
     """The fields of a prompt or decode argument block that say which form of attention is wanted."""
     a.vd = 0 if form.value_dim in (0, head_dim) else form.value_dim
-    a.has_sink, a.sink_score = (0, 0.0) if form.sink is None else (1, form.sink)
+    _set_sink(a, form)
     a.gate = _ptr(gate, torch.float32)
+
+
+def _set_sink(a, form: AttentionForm, n_heads: Optional[int] = None) -> None:
+    a.has_sink, a.sink_score = (0, 0.0) if form.sink is None else (1, form.sink)
+    if form.sinks is not None:
+        if form.sinks.numel() != a.nh:
+            raise KernelError(f"attention: {form.sinks.numel()} sinks for {a.nh} query heads")
+        a.has_sink, a.sinks = 1, _ptr(form.sinks, torch.float32)
+    a.chunked = int(form.chunked)
 
 
 def attn_tc_status() -> int:
@@ -900,7 +1159,7 @@ def attn_decode(q, k_pages, v_pages, page_table, ring_pages, slots, len_before, 
         a.part, a.counters, a.out = _ptr(scratch), _ptr(counters, torch.int32), _ptr(out, torch.bfloat16)
         a.n_seqs, a.nh, a.nkv, a.hd = b, nh, nkv, hd
         a.scale, a.window = float(scale), int(window)
-        a.has_sink, a.sink_score = (0, 0.0) if form.sink is None else (1, form.sink)
+        _set_sink(a, form)
         a.gate = _ptr(gate, torch.float32)
         _check(lib, lib.llg_attn_decode_tma(byref(a), _ptr(k_pages, torch.bfloat16), _ptr(v_pages, torch.bfloat16),
                                             k_pages.shape[0], int(plan.max_len), _stream()))
