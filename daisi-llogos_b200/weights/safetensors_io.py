@@ -152,4 +152,4 @@ def write_safetensors(path: str, tensors: Mapping[str, torch.Tensor], metadata: 
         f.write(blob)
         for name in order:
             t = tensors[name].detach().contiguous().cpu()
-            f.write(t.view(torch.uint8).numpy().tobytes() if t.numel() else b"")
+            f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b"")

@@ -138,15 +138,22 @@ def expert(h, w, p):
 
 
 def route(h, w, p, top: int):
-    """(chosen experts [T, top], their weights [T, top])."""
+    """(chosen experts [T, top], their weights [T, top], by how much the last chosen logit beats the best one left
+    out [T]; infinite where every expert is chosen)."""
     z = linear(h, w[p + "router"]) + w[p + "router.b"].to(F64)
     val, idx = torch.topk(z, top, dim=-1)
-    return idx, torch.softmax(val, dim=-1)
+    if top < z.shape[-1]:
+        margin = val[:, -1] - torch.topk(z, top + 1, dim=-1).values[:, -1]
+    else:
+        margin = torch.full((z.shape[0],), math.inf, dtype=F64)
+    return idx, torch.softmax(val, dim=-1), margin
 
 
-def moe(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, ml: dict) -> torch.Tensor:
+def moe(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, ml: dict, margins: Optional[list] = None) -> torch.Tensor:
     n_exp, top = int(ml["router"]["experts"]), int(ml["router"]["top"])
-    idx, wt = route(h, w, p, top)
+    idx, wt, margin = route(h, w, p, top)
+    if margins is not None:
+        margins.append(margin)
     out = torch.zeros(h.shape[0], w[p + "e0.down"].shape[0], dtype=F64)
     for e in range(n_exp):
         hit = idx == e                                      # [T, top]
@@ -160,8 +167,10 @@ def moe(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, ml: dict) -> torch.
 
 # ---- the model ------------------------------------------------------------------------------------
 
-def forward(weights: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int], trace: Optional[list] = None) -> torch.Tensor:
-    """float64 logits [T, vocab] of one whole sequence.  ``trace`` (a list) receives the residual after every layer."""
+def forward(weights: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int], trace: Optional[list] = None,
+            margins: Optional[list] = None) -> torch.Tensor:
+    """float64 logits [T, vocab] of one whole sequence.  ``trace`` (a list) receives the residual after every layer,
+    ``margins`` every router's margins (see ``route``)."""
     w = weights
     eps = float(cfg["norm"]["eps"])
     r = float(cfg["residual_mult"])
@@ -181,7 +190,7 @@ def forward(weights: Dict[str, torch.Tensor], cfg: dict, tokens: Sequence[int], 
         else:
             raise ValueError(f"layer type {layer['type']!r}")
         if layer.get("mlp"):
-            y = y + moe(h, w, p + "mlp.", layer["mlp"])
+            y = y + moe(h, w, p + "mlp.", layer["mlp"], margins)
         x = x + r * y
         if trace is not None:
             trace.append(x.clone())
