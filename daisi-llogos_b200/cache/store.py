@@ -3,7 +3,8 @@
 Layers are put into groups by what they need.  A key/value group is defined by
 (key/value heads, head size, window, value head size): all its layers share one page table per sequence and
 one pool of pages, and each layer has its own key and value pages
-``[n_pages, n_kv, 64, head_dim]`` (the value pages with the value heads' size where that differs).  A group with a window keeps a ring of
+``[n_pages, n_kv, 64, head_dim]`` (the value pages with the value heads' size where that differs; no value pages of
+its own where a mixer's values are its keys).  A group with a window keeps a ring of
 ``ceil(window / 64) + 1`` pages per sequence; a group without keeps every page.  Besides,
 every layer that declares a fixed-size state gets ``[n_slots, *shape]``, zeroed when a
 sequence starts (the reference keeps such state for its recurrent layers, one sequence only:
@@ -75,7 +76,12 @@ class KvGroup:
         shape = (n_pages + 1, need.num_kv_heads, PAGE, need.head_dim)
         v_shape = (n_pages + 1, need.num_kv_heads, PAGE, need.value_dim or need.head_dim)
         self.k = {u: torch.zeros(shape, dtype=dtype, device=device) for u in units}
-        self.v = {u: torch.zeros(v_shape, dtype=dtype, device=device) for u in units}
+        if need.values_in_keys:
+            if need.value_dim not in (0, need.head_dim):
+                raise ValueError("values kept in the keys' pages have the keys' size")
+            self.v = self.k                      # one set of pages is read as keys and as values
+        else:
+            self.v = {u: torch.zeros(v_shape, dtype=dtype, device=device) for u in units}
 
     def pages_needed(self, length: int) -> int:
         return min(pages_for(length), self.ring_pages)
@@ -121,7 +127,8 @@ class KvGroup:
         self.pool.give(pages)
 
     def bytes(self) -> int:
-        return sum(t.numel() * t.element_size() for t in list(self.k.values()) + list(self.v.values()))
+        sets = list(self.k.values()) + ([] if self.v is self.k else list(self.v.values()))
+        return sum(t.numel() * t.element_size() for t in sets)
 
 
 class SequenceCache:

@@ -3,8 +3,9 @@
 //   latent_prep : from the rows of the input product [q of all heads | latent | rotated key part] (float32 partial sums):
 //                 the latent is RMS-normed with its weight, the rotated parts of every query head and the shared key part
 //                 are rotated by the token's position (pairs (i, i + rot_dim/2), tables of cos and sin), and the results are
-//                 written as the attention kernels read them: keys [latent | rotated part] and values [latent] for ONE
-//                 key/value head (packed for a prompt step and/or into the cache pages), the queries' rotated parts behind
+//                 written as the attention kernels read them: keys [latent | rotated part] and, where the caller keeps
+//                 values apart, values [latent] for ONE key/value head (packed for a prompt step and/or into the cache
+//                 pages), the queries' rotated parts behind
 //                 the place where head_linear puts the unrotated parts' products, and the unrotated parts by themselves.
 //   head_linear : y[n][h][:] = W_h x[n][h][:], a small product per (token, head) with one matrix per head; float32 sums.
 //
@@ -66,13 +67,15 @@ __global__ void latent_prep_kernel(LatentPrepArgs a) {
     const int slot = a.slots[a.seq_of_token[n]];
     const long long r = kv_row(a.page_table, a.table_width, a.ring_pages, slot, pos, 0, 1);
     kp = (OT*)a.k_pages + r * kd;
-    vp = (OT*)a.v_pages + r * a.rank;
+    vp = a.v_pages ? (OT*)a.v_pages + r * a.rank : nullptr;
   }
   const WT* w = (const WT*)a.c_norm_w;
   for (int d = lane; d < a.rank; d += 32) {
     const OT c = from_f32<OT>(summed(col + d) * inv * to_f32(w[d]));
-    if (kn) { kn[d] = c; vn[d] = c; }
-    if (kp) { kp[d] = c; vp[d] = c; }
+    if (kn) kn[d] = c;
+    if (vn) vn[d] = c;
+    if (kp) kp[d] = c;
+    if (vp) vp[d] = c;
   }
   for (int i = lane; i < half; i += 32) {
     const float x0 = summed(col + a.rank + i), x1 = summed(col + a.rank + half + i);
@@ -139,9 +142,9 @@ LLG_API int llg_latent_prep(const LatentPrepArgs* args, int out_dtype, cudaStrea
   LLG_REQUIRE(a.n_tokens >= 0 && a.nh > 0 && a.dim > 0 && a.rank > 0 && a.rdim >= 0 && a.rdim % 2 == 0, "latent_prep: bad sizes");
   LLG_REQUIRE(a.n_partials >= 1, "latent_prep: n_partials must be >= 1");
   LLG_REQUIRE(a.rdim == 0 || (a.cos_table && a.sin_table && a.table_positions > 0), "latent_prep: rotated elements need the tables");
-  LLG_REQUIRE(!a.k_pages || (a.v_pages && a.page_table && a.slots && a.seq_of_token && a.ring_pages > 0),
-              "latent_prep: a cache write needs both page stores, page_table, slots and seq_of_token");
-  LLG_REQUIRE(!a.k_new == !a.v_new, "latent_prep: packed keys and values come together");
+  LLG_REQUIRE(!a.k_pages || (a.page_table && a.slots && a.seq_of_token && a.ring_pages > 0),
+              "latent_prep: a cache write needs page_table, slots and seq_of_token");
+  LLG_REQUIRE((!a.v_new || a.k_new) && (!a.v_pages || a.k_pages), "latent_prep: values are written beside keys only");
   if (a.n_tokens == 0) return 0;
   const int warps = 4;
   const long long items = (long long)a.n_tokens * (a.nh + 1);

@@ -7,7 +7,8 @@
 //                 up to whole tiles, and gives every pair its row.  Which row of its expert's run a pair gets depends on
 //                 the order in which the threads arrive; no result depends on it (a row's values come from its own token
 //                 alone, and a token's rows are added in the order of its choices).
-//   grouped products: a block takes one tile of rows (one expert) and 32 outputs.
+//   grouped products: a block takes one tile of rows (one expert) and a run of outputs: bfloat16 with rows that start on
+//                 16-byte boundaries on the tensor cores (mma.sync), everything else on the CUDA cores.
 //   moe_combine : out[n] = sum_k weight[n][k] y[row of (n, k)] + the shared expert's partial sums.
 #include "common.cuh"
 #include "kernel_args.h"
@@ -170,6 +171,134 @@ __global__ void __launch_bounds__(256) grouped_linear_kernel(GroupedLinearArgs a
   }
 }
 
+// ---- the grouped products on the tensor cores (bfloat16) ------------------------------------------------------------
+//
+// A block of four warps takes one tile of LLG_MOE_TILE rows (one expert) and MM_O outputs; the activations' rows (gathered
+// through token_of_row) and the expert's matrix rows arrive in shared memory by 16-byte asynchronous copies, two stages
+// deep, in k-blocks of MM_K; every warp owns MM_O / 4 outputs of all rows and multiplies with mma.sync m16n8k16 (bfloat16
+// in, float32 sums).  GATED: a second matrix's tile beside the first, and silu(first) * second is what is stored.
+constexpr int MM_O = 128, MM_K = 64, MM_PAD = 8;            // MM_PAD halves between rows: fragment loads meet no bank twice
+constexpr int MM_LD = MM_K + MM_PAD;
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* src, bool valid) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+  const int bytes = valid ? 16 : 0;                          // 0: the 16 bytes are filled with zeros, src is not read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename YT, bool GATED>
+__global__ void __launch_bounds__(128) grouped_linear_mma_kernel(GroupedLinearArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ __align__(16) unsigned char mm_smem[];
+  typedef __nv_bfloat16 bf16;
+  constexpr int A_HALVES = LLG_MOE_TILE * MM_LD, B_HALVES = MM_O * MM_LD;
+  constexpr int STAGE_HALVES = A_HALVES + (GATED ? 2 : 1) * B_HALVES;
+  bf16* base = reinterpret_cast<bf16*>(mm_smem);
+  __shared__ int src[LLG_MOE_TILE];
+  const int tile = blockIdx.x;
+  const int e = a.tile_expert[tile];
+  if (e < 0) return;
+  const int r0 = tile * LLG_MOE_TILE, o0 = blockIdx.y * MM_O;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+  if (tid < LLG_MOE_TILE) src[tid] = a.token_of_row ? a.token_of_row[r0 + tid] : r0 + tid;
+  __syncthreads();
+  const bf16* x = (const bf16*)a.x;
+  const bf16* w = (const bf16*)a.w + (long long)e * a.n_out * a.n_in;
+  const bf16* w2 = GATED ? (const bf16*)a.w2 + (long long)e * a.n_out * a.n_in : nullptr;
+  constexpr int CH = MM_K / 8;                                // 16-byte chunks in a row of a k-block
+  auto load_stage = [&](int s, int k0) {
+    bf16* As = base + s * STAGE_HALVES;
+    bf16* Bs = As + A_HALVES;
+    for (int idx = tid; idx < LLG_MOE_TILE * CH; idx += 128) {
+      const int r = idx / CH, c = idx % CH, k = k0 + c * 8;
+      const int sr = src[r];
+      const bool ok = sr >= 0 && k < a.n_in;
+      cp_async16(As + r * MM_LD + c * 8, ok ? x + (long long)sr * a.n_in + k : x, ok);
+    }
+    for (int idx = tid; idx < MM_O * CH; idx += 128) {
+      const int r = idx / CH, c = idx % CH, k = k0 + c * 8, o = o0 + r;
+      const bool ok = o < a.n_out && k < a.n_in;
+      const long long off = ok ? (long long)o * a.n_in + k : 0;
+      cp_async16(Bs + r * MM_LD + c * 8, w + off, ok);
+      if (GATED) cp_async16(Bs + B_HALVES + r * MM_LD + c * 8, w2 + off, ok);
+    }
+  };
+  constexpr int MT = LLG_MOE_TILE / 16, NT = MM_O / 4 / 8;    // 16-row tiles of the block, 8-output tiles of a warp
+  float acc[MT][NT][4], acc2[GATED ? MT : 1][GATED ? NT : 1][4];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        acc[i][j][c] = 0.f;
+        if (GATED) acc2[i][j][c] = 0.f;
+      }
+  const int nkb = (a.n_in + MM_K - 1) / MM_K;
+  load_stage(0, 0);
+  cp_async_commit();
+  for (int kb = 0; kb < nkb; ++kb) {
+    if (kb + 1 < nkb) {
+      load_stage((kb + 1) & 1, (kb + 1) * MM_K);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+    const bf16* As = base + (kb & 1) * STAGE_HALVES;
+    const bf16* Bs = As + A_HALVES + warp * (MM_O / 4) * MM_LD;
+#pragma unroll
+    for (int ks = 0; ks < MM_K; ks += 16) {
+      unsigned af[MT][4];
+#pragma unroll
+      for (int i = 0; i < MT; ++i) {
+        const bf16* ap = As + (i * 16 + g) * MM_LD + ks + 2 * t;
+        af[i][0] = *reinterpret_cast<const unsigned*>(ap);
+        af[i][1] = *reinterpret_cast<const unsigned*>(ap + 8 * MM_LD);
+        af[i][2] = *reinterpret_cast<const unsigned*>(ap + 8);
+        af[i][3] = *reinterpret_cast<const unsigned*>(ap + 8 * MM_LD + 8);
+      }
+#pragma unroll
+      for (int j = 0; j < NT; ++j) {
+        const bf16* bp = Bs + (j * 8 + g) * MM_LD + ks + 2 * t;
+        const unsigned b0 = *reinterpret_cast<const unsigned*>(bp), b1 = *reinterpret_cast<const unsigned*>(bp + 8);
+#pragma unroll
+        for (int i = 0; i < MT; ++i) mma_bf16(acc[i][j], af[i], b0, b1);
+        if (GATED) {
+          const unsigned c0 = *reinterpret_cast<const unsigned*>(bp + B_HALVES), c1 = *reinterpret_cast<const unsigned*>(bp + B_HALVES + 8);
+#pragma unroll
+          for (int i = 0; i < MT; ++i) mma_bf16(acc2[i][j], af[i], c0, c1);
+        }
+      }
+    }
+    __syncthreads();                                          // the stage is free for the copies of the step after next
+  }
+  YT* y = (YT*)a.y;
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int r = r0 + i * 16 + g + (c >> 1) * 8;
+        const int o = o0 + warp * (MM_O / 4) + j * 8 + 2 * t + (c & 1);
+        if (o >= a.n_out) continue;
+        float v = acc[i][j][c];
+        if (GATED) v = v / (1.0f + expf(-v)) * acc2[i][j][c];
+        y[(long long)r * a.n_out + o] = from_f32<YT>(v);
+      }
+}
+
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ row_of_pair,
                                    const float* __restrict__ weight, const float* __restrict__ shared, int n_shared,
                                    long long shared_stride, float* __restrict__ out, int hidden, int top) {
@@ -228,9 +357,31 @@ LLG_API int llg_grouped_linear(const GroupedLinearArgs* args, int x_dtype, int y
   const GroupedLinearArgs& a = *args;
   LLG_REQUIRE(a.rows >= 0 && a.rows % LLG_MOE_TILE == 0 && a.n_in > 0 && a.n_out > 0, "grouped_linear: bad sizes");
   if (a.rows == 0) return 0;
+  const bool gated = a.w2 != nullptr;
+  auto aligned = [](const void* p) { return ((uintptr_t)p & 15u) == 0; };
+  if (x_dtype == LLG_BF16 && a.n_in % 8 == 0 && aligned(a.x) && aligned(a.w) && aligned(a.w2)) {
+    // the tensor-core kernel: 16-byte copies need rows that start on 16-byte boundaries
+    dim3 mgrid(a.rows / LLG_MOE_TILE, (a.n_out + MM_O - 1) / MM_O);
+    LLG_REQUIRE(mgrid.y <= 65535, "grouped_linear: too many outputs");
+    const size_t smem = 2 * (size_t)(LLG_MOE_TILE * MM_LD + (gated ? 2 : 1) * MM_O * MM_LD) * sizeof(__nv_bfloat16);
+#define MMA_LAUNCH(YT, G)                                                                                         \
+  do {                                                                                                            \
+    cudaError_t err = cudaFuncSetAttribute(grouped_linear_mma_kernel<YT, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (err != cudaSuccess) return llg_fail("grouped_linear: shared memory %zu: %s", smem, cudaGetErrorString(err)); \
+    llg_launch(grouped_linear_mma_kernel<YT, G>, mgrid, dim3(128), smem, stream, a);                              \
+  } while (0)
+    if (y_dtype == LLG_BF16) {
+      if (gated) MMA_LAUNCH(__nv_bfloat16, true); else MMA_LAUNCH(__nv_bfloat16, false);
+    } else if (y_dtype == LLG_F32) {
+      if (gated) MMA_LAUNCH(float, true); else MMA_LAUNCH(float, false);
+    } else {
+      return llg_fail("grouped_linear: unsupported output dtype %d", y_dtype);
+    }
+#undef MMA_LAUNCH
+    return llg_check_launch("grouped_linear");
+  }
   dim3 grid(a.rows / LLG_MOE_TILE, (a.n_out + GT_O - 1) / GT_O);
   LLG_REQUIRE(grid.y <= 65535, "grouped_linear: too many outputs");
-  const bool gated = a.w2 != nullptr;
   if (x_dtype == LLG_F32 && y_dtype == LLG_F32) {
     if (gated) llg_launch(grouped_linear_kernel<float, float, float, true>, grid, dim3(256), 0, stream, a);
     else llg_launch(grouped_linear_kernel<float, float, float, false>, grid, dim3(256), 0, stream, a);

@@ -697,7 +697,8 @@ def latent_prep(rows: torch.Tensor, *, n_heads: int, head_dim: int, rot_dim: int
                 seq_of_token: Optional[torch.Tensor] = None, slots: Optional[torch.Tensor] = None) -> None:
     """Preparation for latent attention from the rows of one product, float32 partials ``[P, N, nh (dim + rdim) + rank +
     rdim]``: the latent (``rank`` elements, RMS-normed with ``c_norm_w``) and the rotated shared key part become the
-    token's key ``[rank + rdim]`` and value ``[rank]`` of ONE key/value head (packed and/or into the cache pages); every
+    token's key ``[rank + rdim]`` and, where ``v_new`` / ``v_pages`` are given, value ``[rank]`` of ONE key/value head
+    (packed and/or into the cache pages); every
     query head's unrotated part goes to ``q_plain_out`` ``[N, nh, dim]`` and its rotated part, rotated, to the last
     ``rdim`` elements of ``q_out`` ``[N, nh, rank + rdim]`` (the first ``rank`` are ``head_linear``'s to fill)."""
     lib = _lib("latent")
@@ -718,7 +719,7 @@ def latent_prep(rows: torch.Tensor, *, n_heads: int, head_dim: int, rot_dim: int
     a.q_plain, a.q_out, a.k_new, a.v_new = _ptr(q_plain_out), _ptr(q_out), _ptr(k_new), _ptr(v_new)
     a.k_pages, a.v_pages = _ptr(k_pages), _ptr(v_pages)
     if k_pages is not None:
-        assert k_pages.shape[1] == 1 and k_pages.shape[3] == kd and v_pages.shape[3] == kv_rank
+        assert k_pages.shape[1] == 1 and k_pages.shape[3] == kd and (v_pages is None or v_pages.shape[3] == kv_rank)
     if page_table is not None:
         a.page_table, a.table_width = _ptr(page_table, torch.int32), page_table.shape[1]
     a.ring_pages = ring_pages

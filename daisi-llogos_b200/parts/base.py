@@ -65,12 +65,14 @@ class Branch:
 @dataclass(frozen=True)
 class KvNeed:
     """A mixer keeps keys and values per position: ``window`` = 0 for all of them; ``value_dim`` = 0 for value
-    heads of the key heads' size."""
+    heads of the key heads' size; ``values_in_keys``: a position's value IS its key (or a leading part of it), so one
+    set of pages serves as both (the view's ``v_pages`` is its ``k_pages``)."""
 
     num_kv_heads: int
     head_dim: int
     window: int = 0
     value_dim: int = 0
+    values_in_keys: bool = False
 
 
 @dataclass(frozen=True)

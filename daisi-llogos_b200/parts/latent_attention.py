@@ -10,9 +10,11 @@ Per token the mixer's input ``h`` gives
 Only ``c`` and the rotated key part are kept per position.  The products with ``W_uk`` and ``W_uv`` are moved to the
 query's side (they are linear): ``q_h . W_uk,h c = (W_uk,h^T q_h) . c`` and ``sum_j p_j W_uv,h c_j = W_uv,h sum_j p_j c_j``.
 So attention runs over ONE key/value head whose keys are ``[c | rotated part]`` (``kv_rank + rot_dim`` elements) and
-whose values are ``c`` (``kv_rank`` elements), with queries ``[W_uk,h^T q_h,unrotated | q_h,rotated]``, in the same
-kernels, cache pages and rings as every other attention; the score's scale, the mask (sliding window or chunks) and a
-learned sink per head are parameters.  One kernel (``ops.latent_prep``) adds the input product's partial sums, norms
+whose values are ``c``, with queries ``[W_uk,h^T q_h,unrotated | q_h,rotated]``, in the same kernels, cache pages and
+rings as every other attention; the score's scale, the mask (sliding window or chunks) and a learned sink per head are
+parameters.  The cache holds one row per position: the key's pages are read as the values too (a value head as long as a
+key head, so that the tensor-core kernels take it), and the per-head product with ``W_uv`` reads the first ``kv_rank``
+elements of what attention returns; the rest (the weighted rotated parts) is never looked at.  One kernel (``ops.latent_prep``) adds the input product's partial sums, norms
 the latent, rotates and writes queries, keys and values; ``ops.head_linear`` is the per-head product on either side.
 Norm statistics, angles, scores and softmax weights are float32 whatever the compute type.
 """
@@ -90,10 +92,10 @@ class LatentAttention(Mixer):
         self.c_norm_w = tensors["kv_norm.weight"]
         if self.sink_kind == "learned":
             self.sinks = as_f32(tensors["sink"], self.env)
-        self.form = self.env.ops.AttentionForm(value_dim=self.rank, sinks=self.sinks, chunked=self.mask == "chunk")
+        self.form = self.env.ops.AttentionForm(sinks=self.sinks, chunked=self.mask == "chunk")
 
     def cache_need(self):
-        return KvNeed(1, self.kd, self.window, self.rank)
+        return KvNeed(1, self.kd, self.window, values_in_keys=True)
 
     def forward(self, x, ctx, cache) -> Branch:
         ops = ctx.ops
@@ -105,9 +107,9 @@ class LatentAttention(Mixer):
         common = dict(n_heads=self.nh, head_dim=self.dim, rot_dim=self.rdim, kv_rank=self.rank, c_norm_w=self.c_norm_w,
                       norm_eps=self.eps, cos=rot.cos if rot else None, sin=rot.sin if rot else None,
                       positions=ctx.positions, q_plain_out=q_plain, q_out=q)
-        pages = dict(k_pages=cache.k_pages, v_pages=cache.v_pages, page_table=cache.page_table,
+        pages = dict(k_pages=cache.k_pages, page_table=cache.page_table,
                      ring_pages=cache.ring_pages, seq_of_token=ctx.seq_of_token, slots=ctx.slots)
-        mixed = ctx.buffer("lattn.mixed", (n, self.nh, self.rank))          # sum_j p_j c_j per head
+        mixed = ctx.buffer("lattn.mixed", (n, self.nh, self.kd))            # per head sum_j p_j [c_j | rotated part]
         if ctx.decode:
             ops.latent_prep(rows, **common, **pages)
             ops.head_linear(q_plain, self.w_absorb, q[:, :, :self.rank])
@@ -117,27 +119,26 @@ class LatentAttention(Mixer):
             if plan.n_counters:
                 counters = ctx.buffer("attn.counters", (plan.n_counters,), torch.int32, zero=True)
             ops.attn_decode(q, cache.k_pages, cache.v_pages, cache.page_table, cache.ring_pages, ctx.slots,
-                            ctx.len_before, mixed.view(n, self.nh * self.rank), scratch, scale=self.scale,
+                            ctx.len_before, mixed.view(n, self.nh * self.kd), scratch, scale=self.scale,
                             window=self.window, plan=plan, counters=counters, form=self.form)
         else:
             write_now = self.window == 0
             k_new = ctx.buffer("lattn.k_new", (n, 1, self.kd))
-            v_new = ctx.buffer("lattn.v_new", (n, 1, self.rank))
             if write_now:
-                ops.latent_prep(rows, **common, k_new=k_new, v_new=v_new, **pages)
+                ops.latent_prep(rows, **common, k_new=k_new, **pages)
             else:
-                ops.latent_prep(rows, **common, k_new=k_new, v_new=v_new)
+                ops.latent_prep(rows, **common, k_new=k_new)
             ops.head_linear(q_plain, self.w_absorb, q[:, :, :self.rank])
             tq = ops.prefill_tile_queries(q.dtype, self.kd, self.form)
-            ops.attn_prefill(q, k_new, v_new, cache.k_pages, cache.v_pages, cache.page_table, cache.ring_pages,
+            ops.attn_prefill(q, k_new, k_new, cache.k_pages, cache.v_pages, cache.page_table, cache.ring_pages,
                              ctx.query_tiles(tq), ctx.cu_tokens, ctx.len_before, ctx.slots,
-                             mixed.view(n, self.nh * self.rank), scale=self.scale, window=self.window,
+                             mixed.view(n, self.nh * self.kd), scale=self.scale, window=self.window,
                              tile_queries=tq, form=self.form)
             if not write_now:
-                ops.kv_write(k_new, v_new, cache.k_pages, cache.v_pages, cache.page_table, cache.ring_pages,
+                ops.kv_write(k_new, k_new, cache.k_pages, cache.v_pages, cache.page_table, cache.ring_pages,
                              ctx.positions, ctx.seq_of_token, ctx.slots, ctx.cu_tokens, ctx.len_before)
         out = ctx.buffer("lattn.out", (n, self.nh, self.vdim))
-        ops.head_linear(mixed, self.w_uv, out)
+        ops.head_linear(mixed[:, :, :self.rank], self.w_uv, out)
         return Branch(linear(ctx, out.view(n, self.nh * self.vdim), self.w_o, "lattn.proj", torch.float32))
 
 

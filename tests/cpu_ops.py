@@ -144,6 +144,8 @@ def latent_prep(rows, *, n_heads, head_dim, rot_dim, kv_rank, c_norm_w, norm_eps
         kr = rotate(kr)
     k = torch.cat([c, kr], dim=-1).view(n, 1, kv_rank + rot_dim).to(q_out.dtype)
     v = c.view(n, 1, kv_rank).to(q_out.dtype)
+    if v_new is None and v_pages is None:          # the caller reads its values out of the keys
+        v, v_new, v_pages = k, k_new, k_pages
     _store_kv(k, v, positions, k_new, v_new, k_pages, v_pages, page_table, ring_pages, seq_of_token, slots)
 
 

@@ -41,7 +41,7 @@ def test_spec_names_parts_tensors_and_cache_units(llogos):
     assert model.tensor_decls()["l0.mix.vmix"].shape == () and model.tensor_decls()["l1.mix.uk"].shape == (3 * 16, 24)
     needs = model.cache_needs()
     KvNeed = llogos.parts.base.KvNeed
-    assert needs[0] == KvNeed(2, 16, 37, 24) and needs[1] == KvNeed(1, 24 + 8, 50, 24) and needs[3] == KvNeed(4, 24, 5, 0)
+    assert needs[0] == KvNeed(2, 16, 37, 24) and needs[1] == KvNeed(1, 24 + 8, 50, values_in_keys=True) and needs[3] == KvNeed(4, 24, 5, 0)
     assert [type(b).__name__ for b in model.blocks] == ["ParallelBlock"] * 6
     assert model.spec.head.params["tied_to"] == "embed" and len(model.spec.encodings) == 6
 
