@@ -21,7 +21,9 @@ steps stand for.  The two workloads of a few hundred steps are run twice and the
 records the CUDA graphs of its decode steps inside its decode time); the one of thousands of steps is run once.  ``--no-workloads`` leaves them out.
 
 ``--probe designs`` prints another line instead: the Karitar design beside the closest stock model (Qwen3) at equal layer
-sizes (``--sizes``), prompt and decode throughput of each and every kernel of the two steps against its roofline.
+sizes (``--sizes``), prompt and decode throughput of each and every kernel of the two steps against its roofline;
+``--design fipavik`` puts the Fipavik design (latent and chunked attention, a mixture of experts whose active size is the
+stock model's feed-forward) in Karitar's place.
 """
 import argparse
 import json
@@ -365,9 +367,31 @@ DESIGN_SIZES = {"1b-like": (2048, 32, 8, 64, 8192, 1024, 4096), "8b-like": (4096
 DESIGN_LAYERS, DESIGN_VOCAB = 4, 32000
 
 
-def design_configs(size):
-    """The Karitar configuration of a size and the closest stock model's (Qwen3: grouped-query attention with normed
-    queries and keys and the same window, pre-norm blocks) with the same width, heads, head size and feed-forward size."""
+FIPAVIK_EXPERTS, FIPAVIK_TOP = 16, 4
+
+
+def fipavik_config(size):
+    """Fipavik at a size: latent and chunked layers in turn; key heads and value heads of the stock model's head size
+    (latent: 3/4 of it as the latent, 1/4 rotated, so that a cached row is one head size long); the chunk and the window
+    are the size's window (2,048 where it has none); sixteen experts of an eighth of the stock feed-forward each, four
+    per token, and a shared expert of half of it: a token's active feed-forward is the stock model's."""
+    width, heads, kv, hd, ff, window, _ = DESIGN_SIZES[size]
+    mask = {"size": window or 2048}
+    att = {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": mask,
+           "rot": {"base": 500000.0, "dims": hd // 2}, "v_mix": True}
+    lat = {"heads": heads, "dim": hd, "rot_dim": hd // 4, "vdim": hd, "kv_rank": 3 * hd // 4, "scale": (hd + hd // 4) ** -0.5,
+           "mask": mask, "rot": {"base": 20000.0, "dims": hd // 4}}
+    mlp = {"kind": "moe", "router": {"experts": FIPAVIK_EXPERTS, "top": FIPAVIK_TOP}, "expert": {"ff": ff // 8}, "shared": {"ff": ff // 2}}
+    layers = [{"type": "latent_attention" if i % 2 == 0 else "attention", "mixer": dict(lat if i % 2 == 0 else att), "mlp": dict(mlp)}
+              for i in range(DESIGN_LAYERS)]
+    return {"architecture": "Fipavik", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+            "layers": layers}
+
+
+def design_configs(size, design="karitar"):
+    """The configuration of ``design`` (Karitar or Fipavik) at a size and the closest stock model's (Qwen3: grouped-query
+    attention with normed queries and keys and the same window, pre-norm blocks) with the same width, heads, head size
+    and feed-forward size."""
     width, heads, kv, hd, ff, window, _ = DESIGN_SIZES[size]
     mixer = {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5}
     if window:
@@ -380,11 +404,14 @@ def design_configs(size):
              "vocab_size": DESIGN_VOCAB, "rope_theta": 1000000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": False}
     if window:
         qwen3.update(sliding_window=window, layer_types=["sliding_attention"] * DESIGN_LAYERS)
+    if design == "fipavik":
+        return {"fipavik": fipavik_config(size), "qwen3": qwen3}
     return {"karitar": karitar, "qwen3": qwen3}
 
 
 _TIMED_OPS = ("embed_rows", "add_rmsnorm", "hc_add_rmsnorm", "qk_prep", "qkv_row_prep", "gemm_tc", "gemm_tc_act", "gemm_tc_qkv",
-              "act_rows", "silu_mul", "attn_prefill", "attn_decode", "kv_write")
+              "act_rows", "silu_mul", "attn_prefill", "attn_decode", "kv_write", "add_layernorm", "latent_prep", "head_linear",
+              "moe_route", "moe_plan", "moe_gated", "moe_down", "moe_combine")
 
 
 def _kernel_label(name, args, kw):
@@ -420,15 +447,36 @@ def _kernel_cost(name, args, kw, keys_read):
         streams = residual.shape[0] if residual.dim() == 3 else 1
         per_row = 4 * h * streams * (2 if branch is not None else 1) + (4 * h * branch.shape[0] if branch is not None else 0)
         return m * (per_row + h * out.element_size()), 0.0
-    if name in ("qk_prep", "qkv_row_prep", "kv_write"):
+    if name == "add_layernorm":
+        residual, parts, out = args[0], args[1], args[6]
+        m, h = out.shape
+        return m * (4 * h * (2 if parts else 1) + 4 * h * sum(p.shape[0] for p in parts) + h * out.element_size()), 0.0
+    if name in ("moe_gated", "moe_down"):
+        # the pairs' rows (the layout's filling rows left out) against the matrices of the experts they can reach
+        w = args[3] if name == "moe_gated" else args[2]
+        rows_out = args[5] if name == "moe_gated" else args[3]
+        n_exp, n_out, n_in = w.shape
+        pairs = max(1, rows_out.shape[0] - n_exp * (ops_tile() - 1))
+        mats = 2 if name == "moe_gated" else 1
+        moved = min(n_exp, pairs) * mats * n_out * n_in * w.element_size() + pairs * (n_in * args[0].element_size() + n_out * rows_out.element_size())
+        return moved, 2.0 * mats * pairs * n_out * n_in
+    if name == "head_linear":
+        x, w, y = args
+        return x.numel() * x.element_size() + w.nbytes + y.numel() * y.element_size(), 2.0 * x.shape[0] * w.numel()
+    if name in ("qk_prep", "qkv_row_prep", "kv_write", "latent_prep"):
         # the page stores are arguments, but only the step's rows of them are written
         moved = sum(t.nbytes for t in tensors if t.dim() != 4)
         return moved, 0.0
     return sum(t.nbytes for t in tensors), 0.0
 
 
-def probe_designs(torch, L, ops, pk, sizes, batch):
-    """Prefill and decode throughput of Karitar beside the closest stock model at equal layer sizes, and every kernel of
+def ops_tile():
+    from importlib import import_module
+    return import_module("daisi-llogos_b200.kernels.ops").MOE_TILE_ROWS
+
+
+def probe_designs(torch, L, ops, pk, sizes, batch, which="karitar"):
+    """Prefill and decode throughput of a design (``which``) beside the closest stock model at equal layer sizes, and every kernel of
     the two steps against its roofline (the slower of bytes / copy bandwidth and flops / matrix peak)."""
     os.environ["LLOGOS_RUNNER"] = "0"           # the parts call the kernels one by one, so each call can be timed
     dev = torch.device("cuda:0")
@@ -438,7 +486,7 @@ def probe_designs(torch, L, ops, pk, sizes, batch):
     real = {n: getattr(ops, n) for n in _TIMED_OPS}
     for size in sizes:
         window, context = DESIGN_SIZES[size][5], DESIGN_SIZES[size][6]
-        for design, cfg in design_configs(size).items():
+        for design, cfg in design_configs(size, which).items():
             model = L.weights.random_model(cfg, seed=0, dtype=torch.bfloat16, device=dev, std=0.02)
             out = {}
             for graphs in (True, False):
@@ -556,6 +604,8 @@ def main():
     ap.add_argument("--tokens", type=int, default=0,
                     help="with --probe timeline: the time line of a prompt step of so many tokens instead of a decode step")
     ap.add_argument("--sizes", default=",".join(DESIGN_SIZES), help="with --probe designs: which of " + ", ".join(DESIGN_SIZES))
+    ap.add_argument("--design", choices=["karitar", "fipavik"], default="karitar",
+                    help="with --probe designs: the design that stands beside the closest stock model")
     ap.add_argument("--probe", choices=["decode-attention", "leave-one-out", "timeline", "designs"],
                     help="instead of the bench line, print a table: decode attention alone over batch shapes; what "
                          "the decode step loses when each kernel in turn is left out of the recorded graph; or one "
@@ -585,7 +635,7 @@ def main():
     if args.probe == "leave-one-out":
         return probe_leave_one_out(torch, L, ops, dict(SHAPES[args.shape][1]), args.batch, args.context)
     if args.probe == "designs":
-        return probe_designs(torch, L, ops, pk, [s for s in args.sizes.split(",") if s in DESIGN_SIZES], args.batch)
+        return probe_designs(torch, L, ops, pk, [s for s in args.sizes.split(",") if s in DESIGN_SIZES], args.batch, args.design)
     if args.probe == "timeline":
         return probe_timeline(torch, L, ops, dict(SHAPES[args.shape][1], num_hidden_layers=args.layers or 6),
                               args.batch, args.context, args.tokens)

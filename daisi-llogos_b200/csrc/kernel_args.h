@@ -282,4 +282,10 @@ struct GroupedLinearArgs {
   const void* w2;             // the same shape, or null
   void* y;                    // [rows][n_out]
   int rows, n_in, n_out;
+  // Only the tensor-core kernel reads the rest; all zero gives the layout above.  They let it serve a product with one
+  // matrix per head over parts of wider rows: without tile_expert the group is the grid's z index and the rows are the
+  // n_rows tokens themselves.
+  long long x_row_stride, y_row_stride;       // elements between rows (0: n_in, n_out)
+  long long x_group_stride, y_group_stride;   // elements by which group e's rows are shifted in x and y
+  int n_rows;                                 // without token_of_row: rows from n_rows on are neither read nor written (0: all are)
 };

@@ -70,6 +70,54 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const XT* __restrict__ x
   if (lane < top) weight[(long long)n * top + lane] = ev / total;
 }
 
+// The same choice from logits that a product has left as float32 partial sums [n_partials][n_tokens][n_exp] (the router's
+// matrix product on the tensor cores, where the checkpoint stores the router in the compute type): a warp per token adds
+// the partials and the bias, then chooses and weighs as moe_route does.
+__global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__ logits, int n_partials, long long partial_stride,
+                                                       const float* __restrict__ bias, int* __restrict__ choice,
+                                                       float* __restrict__ weight, int n_tokens, int n_exp, int top) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float sm[];
+  __shared__ float chosen_all[4][LLG_MOE_MAX_TOP];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 4 + warp;
+  if (n >= n_tokens) return;
+  float* z = sm + warp * n_exp;
+  float* chosen = chosen_all[warp];
+  for (int e = lane; e < n_exp; e += 32) {
+    float v = bias ? bias[e] : 0.f;
+    for (int s = 0; s < n_partials; ++s) v += logits[s * partial_stride + (long long)n * n_exp + e];
+    z[e] = v;
+  }
+  __syncwarp();
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int e = lane; e < n_exp; e += 32) {
+      const float v = z[e];
+      if (v > best) { best = v; arg = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      if (ob > best || (ob == best && oa < arg)) { best = ob; arg = oa; }
+    }
+    if (arg == 0x7fffffff) arg = 0;
+    if (lane == 0) {
+      choice[(long long)n * top + k] = arg;
+      chosen[k] = best;
+      z[arg] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  const float m = chosen[0];
+  float ev = lane < top ? expf(chosen[lane] - m) : 0.f;
+  const float total = warp_sum(ev);
+  if (lane < top) weight[(long long)n * top + lane] = ev / total;
+}
+
 __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ choice, int n_pairs, int top, int n_exp,
                                                         int* __restrict__ row_of_pair, int* __restrict__ token_of_row,
                                                         int* __restrict__ tile_expert, int cap) {
@@ -205,13 +253,15 @@ __global__ void __launch_bounds__(128) grouped_linear_mma_kernel(GroupedLinearAr
   bf16* base = reinterpret_cast<bf16*>(mm_smem);
   __shared__ int src[LLG_MOE_TILE];
   const int tile = blockIdx.x;
-  const int e = a.tile_expert[tile];
+  const int e = a.tile_expert ? a.tile_expert[tile] : (int)blockIdx.z;
   if (e < 0) return;
   const int r0 = tile * LLG_MOE_TILE, o0 = blockIdx.y * MM_O;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
-  if (tid < LLG_MOE_TILE) src[tid] = a.token_of_row ? a.token_of_row[r0 + tid] : r0 + tid;
+  if (tid < LLG_MOE_TILE)
+    src[tid] = a.token_of_row ? a.token_of_row[r0 + tid] : (a.n_rows == 0 || r0 + tid < a.n_rows) ? r0 + tid : -1;
   __syncthreads();
-  const bf16* x = (const bf16*)a.x;
+  const long long x_ld = a.x_row_stride ? a.x_row_stride : a.n_in, y_ld = a.y_row_stride ? a.y_row_stride : a.n_out;
+  const bf16* x = (const bf16*)a.x + (long long)e * a.x_group_stride;
   const bf16* w = (const bf16*)a.w + (long long)e * a.n_out * a.n_in;
   const bf16* w2 = GATED ? (const bf16*)a.w2 + (long long)e * a.n_out * a.n_in : nullptr;
   constexpr int CH = MM_K / 8;                                // 16-byte chunks in a row of a k-block
@@ -222,7 +272,7 @@ __global__ void __launch_bounds__(128) grouped_linear_mma_kernel(GroupedLinearAr
       const int r = idx / CH, c = idx % CH, k = k0 + c * 8;
       const int sr = src[r];
       const bool ok = sr >= 0 && k < a.n_in;
-      cp_async16(As + r * MM_LD + c * 8, ok ? x + (long long)sr * a.n_in + k : x, ok);
+      cp_async16(As + r * MM_LD + c * 8, ok ? x + (long long)sr * x_ld + k : x, ok);
     }
     for (int idx = tid; idx < MM_O * CH; idx += 128) {
       const int r = idx / CH, c = idx % CH, k = k0 + c * 8, o = o0 + r;
@@ -283,7 +333,7 @@ __global__ void __launch_bounds__(128) grouped_linear_mma_kernel(GroupedLinearAr
     }
     __syncthreads();                                          // the stage is free for the copies of the step after next
   }
-  YT* y = (YT*)a.y;
+  YT* y = (YT*)a.y + (long long)e * a.y_group_stride;
 #pragma unroll
   for (int i = 0; i < MT; ++i)
 #pragma unroll
@@ -292,10 +342,10 @@ __global__ void __launch_bounds__(128) grouped_linear_mma_kernel(GroupedLinearAr
       for (int c = 0; c < 4; ++c) {
         const int r = r0 + i * 16 + g + (c >> 1) * 8;
         const int o = o0 + warp * (MM_O / 4) + j * 8 + 2 * t + (c & 1);
-        if (o >= a.n_out) continue;
+        if (o >= a.n_out || (a.n_rows && r >= a.n_rows)) continue;
         float v = acc[i][j][c];
         if (GATED) v = v / (1.0f + expf(-v)) * acc2[i][j][c];
-        y[(long long)r * a.n_out + o] = from_f32<YT>(v);
+        y[(long long)r * y_ld + o] = from_f32<YT>(v);
       }
 }
 
@@ -305,7 +355,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
   pdl_launch_dependents();
   pdl_wait();
   const int n = blockIdx.x;
-  for (int d = threadIdx.x; d < hidden; d += blockDim.x) {
+  for (int d = blockIdx.y * blockDim.x + threadIdx.x; d < hidden; d += gridDim.y * blockDim.x) {
     float v = 0.f;
     for (int k = 0; k < top; ++k) {
       const int row = row_of_pair[(long long)n * top + k];
@@ -314,6 +364,30 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
     for (int s = 0; s < n_shared; ++s) v += shared[s * shared_stride + (long long)n * hidden + d];
     out[(long long)n * hidden + d] = v;
   }
+}
+
+// The same with four columns a thread (rows that start on 16-byte boundaries): every load of a thread is independent of
+// the others, so the few rows of a decode step are not a chain of waits.
+__global__ void moe_combine_vec4_kernel(const float* __restrict__ y, const int* __restrict__ row_of_pair,
+                                        const float* __restrict__ weight, const float* __restrict__ shared, int n_shared,
+                                        long long shared_stride, float* __restrict__ out, int hidden, int top) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int n = blockIdx.x;
+  const int d = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
+  if (d >= hidden) return;
+  float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int k = 0; k < top; ++k) {
+    const int row = row_of_pair[(long long)n * top + k];
+    const float wk = weight[(long long)n * top + k];
+    const float4 u = *reinterpret_cast<const float4*>(y + (long long)row * hidden + d);
+    v.x = fmaf(wk, u.x, v.x); v.y = fmaf(wk, u.y, v.y); v.z = fmaf(wk, u.z, v.z); v.w = fmaf(wk, u.w, v.w);
+  }
+  for (int s = 0; s < n_shared; ++s) {
+    const float4 u = *reinterpret_cast<const float4*>(shared + s * shared_stride + (long long)n * hidden + d);
+    v.x += u.x; v.y += u.y; v.z += u.z; v.w += u.w;
+  }
+  *reinterpret_cast<float4*>(out + (long long)n * hidden + d) = v;
 }
 
 }  // namespace
@@ -340,6 +414,18 @@ LLG_API int llg_moe_route(const void* x, int x_dtype, const float* w, const floa
     return llg_fail("moe_route: unknown dtype %d", x_dtype);
   }
   return llg_check_launch("moe_route");
+}
+
+LLG_API int llg_moe_topk(const float* logits, int n_partials, long long partial_stride, const float* bias, int* choice,
+                         float* weight, int n_tokens, int n_exp, int top, cudaStream_t stream) {
+  LLG_REQUIRE(n_tokens >= 0 && n_partials >= 1, "moe_topk: bad sizes");
+  LLG_REQUIRE(n_exp > 0 && n_exp <= LLG_MOE_MAX_EXPERTS, "moe_topk: %d experts are outside [1, %d]", n_exp, LLG_MOE_MAX_EXPERTS);
+  LLG_REQUIRE(top > 0 && top <= n_exp && top <= LLG_MOE_MAX_TOP, "moe_topk: top %d of %d experts (at most %d)", top, n_exp,
+              LLG_MOE_MAX_TOP);
+  if (n_tokens == 0) return 0;
+  llg_launch(moe_topk_kernel, dim3((n_tokens + 3) / 4), dim3(128), (size_t)4 * n_exp * sizeof(float), stream, logits, n_partials,
+             partial_stride, bias, choice, weight, n_tokens, n_exp, top);
+  return llg_check_launch("moe_topk");
 }
 
 LLG_API int llg_moe_plan(const int* choice, int n_pairs, int top, int n_exp, int* row_of_pair, int* token_of_row,
@@ -397,13 +483,57 @@ LLG_API int llg_grouped_linear(const GroupedLinearArgs* args, int x_dtype, int y
   return llg_check_launch("grouped_linear");
 }
 
+// y[n][h][:] = w[h] x[n][h][:] on the tensor cores (bfloat16; x rows on 16-byte boundaries): the grouped kernel with the
+// head as the group.  The caller has checked the alignment (llg_head_linear_mma_supported).
+LLG_API int llg_head_linear_mma_supported(const void* x, long long x_token_stride, long long x_head_stride, const void* w, int n_in) {
+  return n_in % 8 == 0 && x_token_stride % 8 == 0 && x_head_stride % 8 == 0 && ((uintptr_t)x & 15u) == 0 && ((uintptr_t)w & 15u) == 0;
+}
+
+LLG_API int llg_head_linear_mma(const void* x, long long x_token_stride, long long x_head_stride, const void* w, void* y,
+                                long long y_token_stride, long long y_head_stride, int n_tokens, int nh, int n_in, int n_out,
+                                cudaStream_t stream) {
+  LLG_REQUIRE(n_tokens >= 0 && nh > 0 && nh <= 65535 && n_in > 0 && n_out > 0, "head_linear: bad sizes");
+  LLG_REQUIRE(llg_head_linear_mma_supported(x, x_token_stride, x_head_stride, w, n_in),
+              "head_linear: the tensor-core kernel wants rows that start on 16-byte boundaries");
+  if (n_tokens == 0) return 0;
+  GroupedLinearArgs a;
+  memset(&a, 0, sizeof(a));
+  a.x = x;
+  a.w = w;
+  a.y = y;
+  a.rows = (n_tokens + LLG_MOE_TILE - 1) / LLG_MOE_TILE * LLG_MOE_TILE;
+  a.n_in = n_in;
+  a.n_out = n_out;
+  a.x_row_stride = x_token_stride;
+  a.y_row_stride = y_token_stride;
+  a.x_group_stride = x_head_stride;
+  a.y_group_stride = y_head_stride;
+  a.n_rows = n_tokens;
+  dim3 grid(a.rows / LLG_MOE_TILE, (n_out + MM_O - 1) / MM_O, nh);
+  LLG_REQUIRE(grid.y <= 65535, "head_linear: too many outputs");
+  const size_t smem = 2 * (size_t)(LLG_MOE_TILE * MM_LD + MM_O * MM_LD) * sizeof(__nv_bfloat16);
+  cudaError_t err = cudaFuncSetAttribute(grouped_linear_mma_kernel<__nv_bfloat16, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (err != cudaSuccess) return llg_fail("head_linear: shared memory %zu: %s", smem, cudaGetErrorString(err));
+  llg_launch(grouped_linear_mma_kernel<__nv_bfloat16, false>, grid, dim3(128), smem, stream, a);
+  return llg_check_launch("head_linear");
+}
+
 LLG_API int llg_moe_combine(const float* y, const int* row_of_pair, const float* weight, const float* shared, int n_shared,
                             long long shared_stride, float* out, int n_tokens, int hidden, int top, cudaStream_t stream) {
   LLG_REQUIRE(n_tokens >= 0 && hidden > 0 && top > 0, "moe_combine: bad sizes");
   LLG_REQUIRE(!shared || n_shared >= 1, "moe_combine: a shared expert's partials need at least one");
   if (n_tokens == 0) return 0;
-  const int threads = hidden >= 1024 ? 256 : 128;
-  llg_launch(moe_combine_kernel, dim3(n_tokens), dim3(threads), 0, stream, y, row_of_pair, weight, shared, shared ? n_shared : 0,
-             shared_stride, out, hidden, top);
+  const bool vec = hidden % 4 == 0 && shared_stride % 4 == 0 && ((uintptr_t)y % 16) == 0 && ((uintptr_t)shared % 16) == 0 &&
+                   ((uintptr_t)out % 16) == 0;
+  if (vec) {
+    const int threads = 128;
+    dim3 grid(n_tokens, (hidden / 4 + threads - 1) / threads);
+    llg_launch(moe_combine_vec4_kernel, grid, dim3(threads), 0, stream, y, row_of_pair, weight, shared, shared ? n_shared : 0,
+               shared_stride, out, hidden, top);
+  } else {
+    const int threads = hidden >= 1024 ? 256 : 128;
+    llg_launch(moe_combine_kernel, dim3(n_tokens, 1), dim3(threads), 0, stream, y, row_of_pair, weight, shared,
+               shared ? n_shared : 0, shared_stride, out, hidden, top);
+  }
   return llg_check_launch("moe_combine");
 }

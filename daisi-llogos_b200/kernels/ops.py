@@ -219,6 +219,8 @@ class _GroupedLinearArgs(Structure):
     _fields_ = [
         ("x", c_void_p), ("token_of_row", c_void_p), ("tile_expert", c_void_p), ("w", c_void_p), ("w2", c_void_p),
         ("y", c_void_p), ("rows", c_int), ("n_in", c_int), ("n_out", c_int),
+        ("x_row_stride", c_longlong), ("y_row_stride", c_longlong), ("x_group_stride", c_longlong),
+        ("y_group_stride", c_longlong), ("n_rows", c_int),
     ]
 
 
@@ -312,6 +314,10 @@ def _load_lib(name: str):
         lib.llg_head_linear.argtypes = [POINTER(_HeadLinearArgs), c_int, c_void_p]
     elif name == "moe":
         lib.llg_moe_route.argtypes = [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]
+        lib.llg_head_linear_mma_supported.argtypes = [c_void_p, c_longlong, c_longlong, c_void_p, c_int]
+        lib.llg_head_linear_mma.argtypes = [c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong,
+                                            c_int, c_int, c_int, c_int, c_void_p]
+        lib.llg_moe_topk.argtypes = [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
         lib.llg_moe_plan.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
         lib.llg_grouped_linear.argtypes = [POINTER(_GroupedLinearArgs), c_int, c_int, c_void_p]
         lib.llg_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_int,
@@ -730,7 +736,9 @@ def latent_prep(rows: torch.Tensor, *, n_heads: int, head_dim: int, rot_dim: int
 
 def head_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
     """y[n, h, :] = w[h] x[n, h, :]: ``x`` ``[N, nh, a]``, ``w`` ``[nh, b, a]`` (contiguous), ``y`` ``[N, nh, b]``.  ``x`` and
-    ``y`` may be views into wider rows (their last elements contiguous); float32 sums, one dtype for all three."""
+    ``y`` may be views into wider rows (their last elements contiguous); float32 sums, one dtype for all three.
+    bfloat16 with rows on 16-byte boundaries runs on the tensor cores (csrc/moe.cu's grouped kernel), the rest on the CUDA
+    cores (csrc/latent.cu)."""
     lib = _lib("latent")
     n, nh, k = x.shape
     assert w.shape[0] == nh and w.shape[2] == k and y.shape == (n, nh, w.shape[1]), (x.shape, w.shape, y.shape)
@@ -740,6 +748,13 @@ def head_linear(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
         raise KernelError("head_linear: x, w and y must share a dtype")
     if n and (x.stride(2) != 1 or y.stride(2) != 1):
         raise KernelError("head_linear: the innermost elements of x and y must be contiguous")
+    if n and x.dtype == torch.bfloat16:
+        # the grouped tensor-core kernel of the experts, with the head as the group
+        moe = _moe_lib()
+        if moe.llg_head_linear_mma_supported(x.data_ptr(), x.stride(0), x.stride(1), _ptr(w), k):
+            _check(moe, moe.llg_head_linear_mma(x.data_ptr(), x.stride(0), x.stride(1), _ptr(w), y.data_ptr(), y.stride(0),
+                                                y.stride(1), n, nh, k, w.shape[1], _stream()))
+            return
     a = _HeadLinearArgs()
     a.x, a.x_token_stride, a.x_head_stride = x.data_ptr(), x.stride(0), x.stride(1)
     a.w = _ptr(w)
@@ -779,6 +794,17 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, b_router: Optional[torch.
     assert b_router is None or b_router.shape == (n_exp,)
     _check(lib, lib.llg_moe_route(_ptr(x), _dt(x), _ptr(w_router, torch.float32), _ptr(b_router, torch.float32),
                                   _ptr(choice, torch.int32), _ptr(weight, torch.float32), n, hidden, n_exp, top, _stream()))
+
+
+def moe_topk(logits: torch.Tensor, b_router: Optional[torch.Tensor], choice: torch.Tensor, weight: torch.Tensor) -> None:
+    """As ``moe_route``, from router logits that a product has left as float32 partial sums ``[S, N, experts]``: the
+    partials and the bias are added, then the experts are chosen and weighed."""
+    lib = _moe_lib()
+    s, n, n_exp = logits.shape
+    top = choice.shape[1]
+    assert choice.shape == (n, top) and weight.shape == (n, top) and (b_router is None or b_router.shape == (n_exp,))
+    _check(lib, lib.llg_moe_topk(_ptr(logits, torch.float32), s, n * n_exp, _ptr(b_router, torch.float32),
+                                 _ptr(choice, torch.int32), _ptr(weight, torch.float32), n, n_exp, top, _stream()))
 
 
 def moe_plan(choice: torch.Tensor, n_experts: int, row_of_pair: torch.Tensor, token_of_row: torch.Tensor,

@@ -1,6 +1,6 @@
 """A feed-forward of many small experts of which every token uses a few, beside an optional shared expert.
 
-Router: ``z = W_r h + b`` in float32; the ``top`` experts of largest ``z`` are chosen per token and weighted by a
+Router: ``z = W_r h + b`` with float32 sums; the ``top`` experts of largest ``z`` are chosen per token and weighted by a
 softmax over the chosen logits alone.  Every expert is the gated form ``W_down (silu(W_gate h) * W_up h)`` without
 biases; the token's output is the weighted sum of its experts' outputs, plus the shared expert's (which every token
 runs) where the layer has one.
@@ -15,6 +15,7 @@ from __future__ import annotations
 
 import torch
 
+from ..kernels.linear import linear
 from .base import Branch, FeedForward, TensorDecl, as_f32, part_class, register_part
 
 
@@ -80,7 +81,10 @@ class MoeFeedForward(FeedForward):
         return t
 
     def bind(self, tensors):
-        self.w_router = as_f32(tensors["router.weight"], self.env)
+        # A router stored in the compute type goes through the matrix product every other projection takes (the products
+        # of bfloat16 values are exact in float32 and are added in float32); one stored wider keeps its own kernel.
+        self.w_router_same = tensors["router.weight"] if tensors["router.weight"].dtype == self.env.dtype else None
+        self.w_router = as_f32(tensors["router.weight"], self.env) if self.w_router_same is None else None
         self.b_router = as_f32(tensors["router.bias"], self.env) if self.router_bias else None
         per = {what: [tensors[self._expert(i, what)] for i in range(self.n_exp)] for what in ("gate", "up", "down")}
         if len({w.dtype for ws in per.values() for w in ws}) != 1:
@@ -97,7 +101,12 @@ class MoeFeedForward(FeedForward):
         pairs = n * self.top
         choice = ctx.buffer("moe.choice", (n, self.top), torch.int32)
         weight = ctx.buffer("moe.weight", (n, self.top), torch.float32)
-        ops.moe_route(x, self.w_router, self.b_router, choice, weight)
+        if self.w_router_same is not None and x.dtype == self.w_router_same.dtype and hasattr(ops, "moe_topk"):
+            ops.moe_topk(linear(ctx, x, self.w_router_same, "moe.logits", torch.float32), self.b_router, choice, weight)
+        else:
+            if self.w_router is None:
+                self.w_router = as_f32(self.w_router_same, self.env)
+            ops.moe_route(x, self.w_router, self.b_router, choice, weight)
         cap = ops.moe_row_capacity(pairs, self.n_exp)
         row_of_pair = ctx.buffer("moe.row_of_pair", (pairs,), torch.int32)
         token_of_row = ctx.buffer("moe.token_of_row", (cap,), torch.int32)

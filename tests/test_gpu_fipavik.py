@@ -313,6 +313,14 @@ def test_expert_kernels(llogos, dtype, n, hidden, n_exp, top, ff):
     sure = margin > 1e-4
     assert torch.equal(choice.cpu().long()[sure], idx[sure]), "the chosen experts, largest logit first"
     assert float((weight.cpu().double()[sure] - wt[sure]).abs().max()) < 1e-5
+    # the same choice from logits that a product left as partial sums (here: the two halves of the sum over the width)
+    half = hidden // 2
+    parts = torch.stack([x.float()[:, :half] @ w["m.router"][:, :half].t(), x.float()[:, half:] @ w["m.router"][:, half:].t()])
+    choice2 = torch.empty_like(choice)
+    weight2 = torch.empty_like(weight)
+    ops.moe_topk(parts.cuda().contiguous(), w["m.router.b"].cuda(), choice2, weight2)
+    assert torch.equal(choice2.cpu().long()[sure], idx[sure])
+    assert float((weight2.cpu().double()[sure] - wt[sure]).abs().max()) < 1e-5
     # the layout: every pair has a row of its own inside its expert's tiles
     cap = ops.moe_row_capacity(n * top, n_exp)
     row_of_pair = torch.empty((n * top,), dtype=torch.int32, device="cuda")
