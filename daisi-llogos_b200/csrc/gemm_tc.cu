@@ -136,6 +136,11 @@ struct GemmParams {
   RowScale scale;   // of the token rows of x: the result's rows are multiplied by it (EPI 2 / 3 take prep.row_scale)
   int act;          // EPI -1 (the plain epilogue with an activation; one split): kind + 1, every element goes through
                     // llg_act(kind, .) before it is stored.  A variant of its own, so that the plain products carry none of it.
+  // Grouped products (SWAP 1, one token tile per block): token tile t multiplies with the matrix of group tile_group[t],
+  // whose rows start at row tile_group[t] * group_rows of w; a tile whose group is negative is left out by every role.
+  // The list is written by a kernel earlier in the step, so nothing of w is requested ahead of the dependency wait.
+  const int* tile_group;
+  int group_rows;
 };
 
 // The activation of an epilogue on sixteen values.  The square of relu is two instructions a value and stays in line; the
@@ -227,14 +232,17 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
   // row of w that the weight tile `mt` of the block at first-operand offset o0 starts at
   auto w_row = [&](int o0, int mt) { return GATED_ROWS ? mt * p.up_offset + o0 : o0 + mt * BM; };
   // second operand: one box of TN rows, or (gated, tokens first) the gate half and the up half of the features
-  auto load_second = [&](unsigned char* dst, int kb, int n0, uint64_t* bar) {
+  auto load_second = [&](unsigned char* dst, int kb, int n0, uint64_t* bar, int row0 = 0) {
     if (EPI == 1 && SWAP == 1) {
-      tma_load_2d(dst, &map_x, kb * BK, n0 / 2, bar);
-      tma_load_2d(dst + (TN / 2) * BK * 2, &map_x, kb * BK, p.up_offset + n0 / 2, bar);
+      tma_load_2d(dst, &map_x, kb * BK, row0 + n0 / 2, bar);
+      tma_load_2d(dst + (TN / 2) * BK * 2, &map_x, kb * BK, row0 + p.up_offset + n0 / 2, bar);
     } else {
-      tma_load_2d(dst, &map_x, kb * BK, n0, bar);
+      tma_load_2d(dst, &map_x, kb * BK, row0 + n0, bar);
     }
   };
+  const bool grouped = SWAP == 1 && MT == 1 && p.tile_group != nullptr;
+  // the group of a tile's tokens (read only after the dependency wait)
+  auto group_of = [&](int tile) { return p.tile_group[tile % m_tiles]; };
   // first operand: MT tiles of 128 rows
   auto load_first = [&](unsigned char* dst, int kb, int o0, uint64_t* bar) {
 #pragma unroll
@@ -265,7 +273,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
     // first ring of weight tiles is on its way before the block's tensor memory is there and long before this kernel
     // waits for its predecessor.  The weights are the first operand of a decode step's product and the second of a
     // prompt step's.
-    if ((int)blockIdx.x < total_tiles) {
+    if ((int)blockIdx.x < total_tiles && !grouped) {
       const int o0 = first_offset(blockIdx.x), n0 = second_offset(blockIdx.x);
       pre = min(nkb, STAGES);
       for (int i = 0; i < pre; ++i) {
@@ -293,8 +301,15 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
     if (lane == 0) {
       int it = 0;                 // k-blocks requested so far
       bool first = true;
+      if (grouped) pdl_wait();    // the list of groups is another kernel's
       for (int tile = blockIdx.x; tile < total_tiles && !*abortp; tile += gridDim.x) {
         const int o0 = first_offset(tile), n0 = second_offset(tile);
+        int w_row0 = 0;
+        if (grouped) {
+          const int grp = group_of(tile);
+          if (grp < 0) continue;
+          w_row0 = grp * p.group_rows;
+        }
         int done = 0;
         if (first) {
           // the first tile's weight tiles are on their way (above); its activation tiles follow the dependency wait
@@ -317,7 +332,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
           mbar_expect_tx(&full_bar[s], stage_tx);
           unsigned char* a = smem + s * STAGE_BYTES;
           load_first(a, kb0 + i, o0, &full_bar[s]);
-          load_second(a + A_BYTES, kb0 + i, n0, &full_bar[s]);
+          load_second(a + A_BYTES, kb0 + i, n0, &full_bar[s], w_row0);
         }
       }
       if (*abortp) {
@@ -336,7 +351,9 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
     if (lane == 0) {
       constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
       int it = 0, round = 0;
+      if (grouped) pdl_wait();
       for (int tile = blockIdx.x; tile < total_tiles && !*abortp; tile += gridDim.x, ++round) {
+        if (grouped && group_of(tile) < 0) { --round; continue; }      // left out by every role alike
         const int b = round % NACC;
         if (round >= NACC && !mbar_wait(&acc_empty[b], ((round / NACC) - 1) & 1, abortp)) {
           if (!*abortp) { *abortp = 1; atomicCAS(&g_error, 0, 3); }
@@ -373,6 +390,7 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
     pdl_wait();                 // before anything of the previous kernel is read or overwritten
     int round = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++round) {
+      if (grouped && group_of(tile) < 0) { --round; continue; }
       const int o0 = first_offset(tile), n0 = second_offset(tile);
       const int b = round % NACC;
       const float* col_scale = col_scales[round & 1];
@@ -860,6 +878,32 @@ static int gemm_tc_run(const void* x, const void* w, void* out, int out_dtype, i
 #undef GATED
 #undef PLAIN
 #undef WIDE
+}
+
+// Grouped product on the tensor cores: out[r][:] = w[group of r's tile] x[r][:] for `rows` rows (a multiple of 128) whose
+// tiles of 128 rows each belong to one group (tile_group[t], negative: the tile is left out and its rows of out are not
+// written).  w holds the groups' matrices one after another, group_rows rows each: plain rows (o of them, out float32 or
+// bfloat16) or, with gated_features, the gated layout (gate rows filled up to a multiple of 128, then the up rows; out is
+// [rows][gated_features] = silu(gate) * up).  Tokens are the tensor cores' rows, as in a prompt step's products.
+LLG_API int llg_gemm_tc_grouped(const void* x, const void* w, void* out, int out_dtype, int rows, int o, int k, int gated_features,
+                                const int* tile_group, int n_groups, int group_rows, cudaStream_t stream) {
+  LLG_REQUIRE(rows > 0 && rows % BM == 0, "gemm_tc_grouped: %d rows are no multiple of %d", rows, BM);
+  LLG_REQUIRE(tile_group != nullptr && n_groups > 0 && group_rows >= o, "gemm_tc_grouped: needs the tiles' groups and their rows of w");
+  LLG_REQUIRE(llg_gemm_tc_supported(x, w, rows, o, k), "gemm_tc_grouped: needs k %% 8 == 0 and 16-byte aligned operands (k=%d)", k);
+  const bool gated = gated_features > 0;
+  LLG_REQUIRE(!gated || (o == ((gated_features + BM - 1) / BM) * 2 * BM && out_dtype == LLG_BF16),
+              "gemm_tc_grouped: the gated epilogue needs ceil(features / 128) * 256 rows of w per group and bfloat16 output");
+  LLG_REQUIRE((long long)n_groups * group_rows < 2147483647LL, "gemm_tc_grouped: too many rows of w");
+  const int nkb = (k + BK - 1) / BK;
+  const RowScale rs{nullptr, 0, 0.f, 0.f};
+  GemmParams ps{out, /*n=*/o, /*o=*/rows, k, nkb, gated_features, o / 2, BM, QkPrepArgs{}, rs, 0, tile_group, group_rows};
+  CUtensorMap map_w, map_x;
+  LLG_REQUIRE(tensor_map(x, rows, k, BM, &map_x) && tensor_map(w, n_groups * group_rows, k, gated ? 128 : 256, &map_w),
+              "gemm_tc_grouped: cuTensorMapEncodeTiled failed or is not available");
+  if (gated) return launch<256, 4, __nv_bfloat16, 1, 1, 1>(&map_x, &map_w, ps, 1, stream);
+  if (out_dtype == LLG_F32) return launch<256, 4, float, 1, 0, 1>(&map_x, &map_w, ps, 1, stream);
+  if (out_dtype == LLG_BF16) return launch<256, 4, __nv_bfloat16, 1, 0, 1>(&map_x, &map_w, ps, 1, stream);
+  return llg_fail("gemm_tc_grouped: unknown output dtype %d", out_dtype);
 }
 
 // 1 when llg_gemm_tc_qkv takes this q/k/v projection: 256 tokens or more (tokens are the tensor cores' rows), head

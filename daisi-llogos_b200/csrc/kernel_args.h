@@ -266,8 +266,9 @@ struct HeadLinearArgs {
 };
 
 // Mixture of experts (moe.cu).  The step's (token, choice) pairs are laid out as rows in the order of their experts, every
-// expert's run filled up to whole tiles of LLG_MOE_TILE rows: row_of_pair[p] is pair p's row, token_of_row[r] the token
-// whose activations row r reads (-1: a filling row), tile_expert[t] the expert of tile t's rows (-1: an unused tile).
+// expert's run filled up to whole tiles of `tile` rows (LLG_MOE_TILE for the kernels of moe.cu, 128 for the grouped tcgen05
+// product): row_of_pair[p] is pair p's row, token_of_row[r] the token whose activations row r reads (-1: a filling row),
+// tile_expert[t] the expert of tile t's rows (-1: an unused tile).
 #define LLG_MOE_TILE 32
 #define LLG_MOE_MAX_EXPERTS 1024
 #define LLG_MOE_MAX_TOP 32
@@ -288,4 +289,5 @@ struct GroupedLinearArgs {
   long long x_row_stride, y_row_stride;       // elements between rows (0: n_in, n_out)
   long long x_group_stride, y_group_stride;   // elements by which group e's rows are shifted in x and y
   int n_rows;                                 // without token_of_row: rows from n_rows on are neither read nor written (0: all are)
+  long long w_group_stride;                   // elements between the groups' matrices in w and w2 (0: n_out * n_in)
 };

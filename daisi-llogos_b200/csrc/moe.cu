@@ -120,14 +120,14 @@ __global__ void __launch_bounds__(128) moe_topk_kernel(const float* __restrict__
 
 __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ choice, int n_pairs, int top, int n_exp,
                                                         int* __restrict__ row_of_pair, int* __restrict__ token_of_row,
-                                                        int* __restrict__ tile_expert, int cap) {
+                                                        int* __restrict__ tile_expert, int cap, int tile_rows) {
   pdl_launch_dependents();
   pdl_wait();
   __shared__ int counts[LLG_MOE_MAX_EXPERTS], starts[LLG_MOE_MAX_EXPERTS], cursor[LLG_MOE_MAX_EXPERTS];
   const int tid = threadIdx.x, nt = blockDim.x;
   for (int e = tid; e < n_exp; e += nt) counts[e] = cursor[e] = 0;
   for (int r = tid; r < cap; r += nt) token_of_row[r] = -1;
-  for (int t = tid; t < cap / LLG_MOE_TILE; t += nt) tile_expert[t] = -1;
+  for (int t = tid; t < cap / tile_rows; t += nt) tile_expert[t] = -1;
   __syncthreads();
   for (int p = tid; p < n_pairs; p += nt) {
     const int e = choice[p];
@@ -138,12 +138,12 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(const int* __restrict__ 
     int at = 0;
     for (int e = 0; e < n_exp; ++e) {
       starts[e] = at;
-      at += (counts[e] + LLG_MOE_TILE - 1) / LLG_MOE_TILE * LLG_MOE_TILE;
+      at += (counts[e] + tile_rows - 1) / tile_rows * tile_rows;
     }
   }
   __syncthreads();
   for (int e = tid; e < n_exp; e += nt) {
-    const int t0 = starts[e] / LLG_MOE_TILE, t1 = t0 + (counts[e] + LLG_MOE_TILE - 1) / LLG_MOE_TILE;
+    const int t0 = starts[e] / tile_rows, t1 = t0 + (counts[e] + tile_rows - 1) / tile_rows;
     for (int t = t0; t < t1; ++t) tile_expert[t] = e;
   }
   for (int p = tid; p < n_pairs; p += nt) {
@@ -174,8 +174,9 @@ __global__ void __launch_bounds__(256) grouped_linear_kernel(GroupedLinearArgs a
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   if (threadIdx.x < LLG_MOE_TILE) src[threadIdx.x] = a.token_of_row ? a.token_of_row[r0 + threadIdx.x] : r0 + threadIdx.x;
   const XT* x = (const XT*)a.x;
-  const WT* w = (const WT*)a.w + (long long)e * a.n_out * a.n_in;
-  const WT* w2 = GATED ? (const WT*)a.w2 + (long long)e * a.n_out * a.n_in : nullptr;
+  const long long w_gs = a.w_group_stride ? a.w_group_stride : (long long)a.n_out * a.n_in;
+  const WT* w = (const WT*)a.w + e * w_gs;
+  const WT* w2 = GATED ? (const WT*)a.w2 + e * w_gs : nullptr;
   constexpr int RPT = LLG_MOE_TILE / 8;             // rows per thread
   float acc[RPT], acc2[RPT];
 #pragma unroll
@@ -262,8 +263,9 @@ __global__ void __launch_bounds__(128) grouped_linear_mma_kernel(GroupedLinearAr
   __syncthreads();
   const long long x_ld = a.x_row_stride ? a.x_row_stride : a.n_in, y_ld = a.y_row_stride ? a.y_row_stride : a.n_out;
   const bf16* x = (const bf16*)a.x + (long long)e * a.x_group_stride;
-  const bf16* w = (const bf16*)a.w + (long long)e * a.n_out * a.n_in;
-  const bf16* w2 = GATED ? (const bf16*)a.w2 + (long long)e * a.n_out * a.n_in : nullptr;
+  const long long w_gs = a.w_group_stride ? a.w_group_stride : (long long)a.n_out * a.n_in;
+  const bf16* w = (const bf16*)a.w + e * w_gs;
+  const bf16* w2 = GATED ? (const bf16*)a.w2 + e * w_gs : nullptr;
   constexpr int CH = MM_K / 8;                                // 16-byte chunks in a row of a k-block
   auto load_stage = [&](int s, int k0) {
     bf16* As = base + s * STAGE_HALVES;
@@ -349,6 +351,19 @@ __global__ void __launch_bounds__(128) grouped_linear_mma_kernel(GroupedLinearAr
       }
 }
 
+// out[r] = x[token_of_row[r]] (zeros for a filling row): the rows of the layout as one matrix, for a product that reads its
+// first operand by tensor copies.  16 bytes a thread.
+__global__ void moe_gather_rows_kernel(const uint4* __restrict__ x, const int* __restrict__ token_of_row, uint4* __restrict__ out,
+                                       int rows, int chunks) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)rows * chunks) return;
+  const int r = (int)(i / chunks), c = (int)(i % chunks);
+  const int t = token_of_row[r];
+  out[i] = t >= 0 ? x[(long long)t * chunks + c] : make_uint4(0u, 0u, 0u, 0u);
+}
+
 __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ row_of_pair,
                                    const float* __restrict__ weight, const float* __restrict__ shared, int n_shared,
                                    long long shared_stride, float* __restrict__ out, int hidden, int top) {
@@ -429,13 +444,15 @@ LLG_API int llg_moe_topk(const float* logits, int n_partials, long long partial_
 }
 
 LLG_API int llg_moe_plan(const int* choice, int n_pairs, int top, int n_exp, int* row_of_pair, int* token_of_row,
-                         int* tile_expert, int cap, cudaStream_t stream) {
+                         int* tile_expert, int cap, int tile_rows, cudaStream_t stream) {
+  LLG_REQUIRE(tile_rows > 0, "moe_plan: tiles of %d rows", tile_rows);
   LLG_REQUIRE(n_exp > 0 && n_exp <= LLG_MOE_MAX_EXPERTS, "moe_plan: %d experts are outside [1, %d]", n_exp, LLG_MOE_MAX_EXPERTS);
   LLG_REQUIRE(top > 0 && n_pairs >= 0 && n_pairs % top == 0, "moe_plan: %d pairs, top %d", n_pairs, top);
-  const long long need = ((long long)n_pairs + (long long)n_exp * (LLG_MOE_TILE - 1) + LLG_MOE_TILE - 1) / LLG_MOE_TILE * LLG_MOE_TILE;
-  LLG_REQUIRE(cap % LLG_MOE_TILE == 0 && cap >= need, "moe_plan: %d rows, %lld needed (whole tiles)", cap, need);
+  const long long need = ((long long)n_pairs + (long long)n_exp * (tile_rows - 1) + tile_rows - 1) / tile_rows * tile_rows;
+  LLG_REQUIRE(cap % tile_rows == 0 && cap >= need, "moe_plan: %d rows, %lld needed (whole tiles)", cap, need);
   if (n_pairs == 0) return 0;
-  llg_launch(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, choice, n_pairs, top, n_exp, row_of_pair, token_of_row, tile_expert, cap);
+  llg_launch(moe_plan_kernel, dim3(1), dim3(1024), 0, stream, choice, n_pairs, top, n_exp, row_of_pair, token_of_row, tile_expert, cap,
+             tile_rows);
   return llg_check_launch("moe_plan");
 }
 
@@ -516,6 +533,17 @@ LLG_API int llg_head_linear_mma(const void* x, long long x_token_stride, long lo
   if (err != cudaSuccess) return llg_fail("head_linear: shared memory %zu: %s", smem, cudaGetErrorString(err));
   llg_launch(grouped_linear_mma_kernel<__nv_bfloat16, false>, grid, dim3(128), smem, stream, a);
   return llg_check_launch("head_linear");
+}
+
+LLG_API int llg_moe_gather_rows(const void* x, const int* token_of_row, void* out, int rows, int row_bytes, cudaStream_t stream) {
+  LLG_REQUIRE(rows >= 0 && row_bytes > 0 && row_bytes % 16 == 0 && ((uintptr_t)x & 15u) == 0 && ((uintptr_t)out & 15u) == 0,
+              "moe_gather_rows: rows of %d bytes must be whole 16-byte pieces on 16-byte boundaries", row_bytes);
+  if (rows == 0) return 0;
+  const int chunks = row_bytes / 16;
+  const long long total = (long long)rows * chunks;
+  llg_launch(moe_gather_rows_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, (const uint4*)x, token_of_row,
+             (uint4*)out, rows, chunks);
+  return llg_check_launch("moe_gather_rows");
 }
 
 LLG_API int llg_moe_combine(const float* y, const int* row_of_pair, const float* weight, const float* shared, int n_shared,

@@ -220,7 +220,7 @@ class _GroupedLinearArgs(Structure):
         ("x", c_void_p), ("token_of_row", c_void_p), ("tile_expert", c_void_p), ("w", c_void_p), ("w2", c_void_p),
         ("y", c_void_p), ("rows", c_int), ("n_in", c_int), ("n_out", c_int),
         ("x_row_stride", c_longlong), ("y_row_stride", c_longlong), ("x_group_stride", c_longlong),
-        ("y_group_stride", c_longlong), ("n_rows", c_int),
+        ("y_group_stride", c_longlong), ("n_rows", c_int), ("w_group_stride", c_longlong),
     ]
 
 
@@ -286,6 +286,8 @@ def _load_lib(name: str):
         lib.llg_gemm_tc.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                     POINTER(_RowScale), c_void_p]
         lib.llg_gemm_tc_qkv.argtypes = [c_void_p, c_void_p, c_int, c_int, POINTER(_QkPrepArgs), c_void_p]
+        lib.llg_gemm_tc_grouped.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                                            c_int, c_void_p]
         lib.llg_gemm_tc_act.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                         POINTER(_RowScale), c_void_p]
     elif name == "attention_simt":
@@ -318,7 +320,8 @@ def _load_lib(name: str):
         lib.llg_head_linear_mma.argtypes = [c_void_p, c_longlong, c_longlong, c_void_p, c_void_p, c_longlong, c_longlong,
                                             c_int, c_int, c_int, c_int, c_void_p]
         lib.llg_moe_topk.argtypes = [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
-        lib.llg_moe_plan.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+        lib.llg_moe_plan.argtypes = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
+        lib.llg_moe_gather_rows.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]
         lib.llg_grouped_linear.argtypes = [POINTER(_GroupedLinearArgs), c_int, c_int, c_void_p]
         lib.llg_moe_combine.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_int,
                                         c_int, c_void_p]
@@ -777,10 +780,22 @@ def _moe_lib():
     return lib
 
 
-def moe_row_capacity(pairs: int, n_experts: int) -> int:
+MOE_TC_TILE_ROWS = 128      # rows of a tile of the grouped tcgen05 product (the tensor cores' rows)
+
+
+def moe_tile_rows(dtype: torch.dtype, pairs: int, n_experts: int, hidden: int, inner: int) -> int:
+    """The tile size for a step's layout: the tensor cores' 128 rows where the experts' products can run as the grouped
+    tcgen05 product (bfloat16, row lengths the tensor copies take) and the step brings enough pairs that filling every
+    expert's run up to 128 rows costs little; else the small tile of the kernels in csrc/moe.cu."""
+    if dtype == torch.bfloat16 and hidden % 8 == 0 and inner % 8 == 0 and pairs >= 2 * n_experts * MOE_TC_TILE_ROWS:
+        return MOE_TC_TILE_ROWS
+    return MOE_TILE_ROWS
+
+
+def moe_row_capacity(pairs: int, n_experts: int, tile: int = MOE_TILE_ROWS) -> int:
     """Rows that the (token, choice) pairs of a step can take once every expert's run is filled up to whole tiles."""
-    cap = pairs + n_experts * (MOE_TILE_ROWS - 1)
-    return -(-cap // MOE_TILE_ROWS) * MOE_TILE_ROWS
+    cap = pairs + n_experts * (tile - 1)
+    return -(-cap // tile) * tile
 
 
 def moe_route(x: torch.Tensor, w_router: torch.Tensor, b_router: Optional[torch.Tensor], choice: torch.Tensor,
@@ -812,43 +827,88 @@ def moe_plan(choice: torch.Tensor, n_experts: int, row_of_pair: torch.Tensor, to
     """Lays the pairs ``(n, k)`` of ``choice`` ``[N, top]`` out as rows in the order of their experts, every expert's run
     filled up to whole tiles of ``MOE_TILE_ROWS``: ``row_of_pair[n * top + k]`` the pair's row, ``token_of_row[r]`` the
     row's token (-1: a filling row), ``tile_expert[t]`` the expert of tile t (-1: unused).  ``token_of_row`` has
-    ``moe_row_capacity(N * top, n_experts)`` entries."""
+    ``moe_row_capacity(N * top, n_experts, tile)`` entries and ``tile_expert`` one per tile: their sizes say which tile
+    size is meant."""
     lib = _moe_lib()
     n, top = choice.shape
     cap = token_of_row.numel()
-    assert row_of_pair.numel() == n * top and tile_expert.numel() * MOE_TILE_ROWS == cap
+    tile = _tile_of(cap, tile_expert)
+    assert row_of_pair.numel() == n * top
     _check(lib, lib.llg_moe_plan(_ptr(choice, torch.int32), n * top, top, n_experts, _ptr(row_of_pair, torch.int32),
-                                 _ptr(token_of_row, torch.int32), _ptr(tile_expert, torch.int32), cap, _stream()))
+                                 _ptr(token_of_row, torch.int32), _ptr(tile_expert, torch.int32), cap, tile, _stream()))
 
 
-def _grouped(x, token_of_row, tile_expert, w, w2, y) -> None:
+def _tile_of(rows: int, tile_expert: torch.Tensor) -> int:
+    tiles = tile_expert.numel()
+    if tiles == 0 or rows % tiles or rows // tiles not in (MOE_TILE_ROWS, MOE_TC_TILE_ROWS):
+        raise KernelError(f"a layout of {rows} rows in {tiles} tiles: tiles have {MOE_TILE_ROWS} or {MOE_TC_TILE_ROWS} rows")
+    return rows // tiles
+
+
+def moe_gather_rows(x: torch.Tensor, token_of_row: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r] = x[token_of_row[r]], zeros for a filling row: the layout's rows as one matrix (for the grouped tcgen05
+    product, whose operands arrive by tensor copies)."""
     lib = _moe_lib()
-    rows, n_out = y.shape
+    rows, width = out.shape
+    assert x.shape[1] == width and x.dtype == out.dtype and token_of_row.numel() == rows
+    _check(lib, lib.llg_moe_gather_rows(_ptr(x), _ptr(token_of_row, torch.int32), _ptr(out), rows, width * x.element_size(), _stream()))
+
+
+def _grouped_tc(x, tile_expert, w, out, gated_features: int) -> None:
+    lib = _lib("gemm_tc")
+    rows, k = x.shape
+    n_groups, group_rows, k2 = w.shape
+    assert k == k2 and tile_expert.numel() * MOE_TC_TILE_ROWS == rows
+    _check(lib, lib.llg_gemm_tc_grouped(_ptr(x, torch.bfloat16), _ptr(w, torch.bfloat16), _ptr(out), _dt(out), rows, group_rows, k,
+                                        gated_features, _ptr(tile_expert, torch.int32), n_groups, group_rows, _stream()))
+
+
+def _grouped(x, token_of_row, tile_expert, w, w2_offset, n_out, y) -> None:
+    """The kernels of csrc/moe.cu: ``w`` ``[E, rows per expert, n_in]``, of which the first ``n_out`` rows of an expert are the
+    (first) matrix and, with ``w2_offset``, the rows from there on the second."""
+    lib = _moe_lib()
+    rows = y.shape[0]
     n_in = x.shape[1]
-    assert w.dim() == 3 and w.shape[1:] == (n_out, n_in) and (w2 is None or w2.shape == w.shape)
+    assert w.dim() == 3 and w.shape[2] == n_in and y.shape[1] == n_out and w.shape[1] >= n_out + (w2_offset or 0)
     assert tile_expert.numel() * MOE_TILE_ROWS == rows and (token_of_row is None or token_of_row.numel() == rows)
     assert token_of_row is not None or x.shape[0] == rows
-    if x.dtype != w.dtype or (w2 is not None and w2.dtype != w.dtype):
+    if x.dtype != w.dtype:
         raise KernelError("grouped products: activations and matrices must share a dtype")
     a = _GroupedLinearArgs()
     a.x, a.token_of_row, a.tile_expert = _ptr(x), _ptr(token_of_row, torch.int32), _ptr(tile_expert, torch.int32)
-    a.w, a.w2, a.y = _ptr(w), _ptr(w2), _ptr(y)
+    a.w, a.y = _ptr(w), _ptr(y)
+    a.w2 = (a.w + w2_offset * n_in * w.element_size()) if w2_offset else None
     a.rows, a.n_in, a.n_out = rows, n_in, n_out
+    a.w_group_stride = w.shape[1] * n_in
     _check(lib, lib.llg_grouped_linear(byref(a), _dt(x), _dt(y), _stream()))
 
 
-def moe_gated(x: torch.Tensor, token_of_row: torch.Tensor, tile_expert: torch.Tensor, w_gate: torch.Tensor,
-              w_up: torch.Tensor, act: torch.Tensor) -> None:
-    """act[r] = silu(w_gate[e] x[t]) * (w_up[e] x[t]) for every row r of the layout (t its token, e its tile's expert);
-    filling rows of a used tile get zeros.  ``w_gate``, ``w_up`` ``[E, inner, hidden]``; ``act`` ``[rows, inner]``."""
-    _grouped(x, token_of_row, tile_expert, w_gate, w_up, act)
+def moe_gated(x: torch.Tensor, token_of_row: Optional[torch.Tensor], tile_expert: torch.Tensor, w_gate_up: torch.Tensor,
+              act: torch.Tensor) -> None:
+    """act[r] = silu(gate_e x_r) * (up_e x_r) for every row r of the layout (e its tile's expert); filling rows of a used
+    tile get zeros.  ``w_gate_up`` ``[E, 2 P, hidden]`` holds every expert's matrices in the gated layout (gate rows,
+    filled up to P = a multiple of 128, then the up rows); ``act`` ``[rows, inner]``.  With tiles of ``MOE_TILE_ROWS``,
+    ``x`` is the step's activations and ``token_of_row`` says which row reads which; with tiles of ``MOE_TC_TILE_ROWS``,
+    ``x`` is the gathered rows themselves (``moe_gather_rows``) and the product runs on tcgen05."""
+    rows, inner = act.shape
+    pad = w_gate_up.shape[1] // 2
+    assert w_gate_up.shape[1] == gated_rows(inner)
+    if _tile_of(rows, tile_expert) == MOE_TC_TILE_ROWS:
+        if token_of_row is not None or x.shape[0] != rows:
+            raise KernelError("moe_gated: tiles of 128 rows take the gathered rows")
+        _grouped_tc(x, tile_expert, w_gate_up, act, inner)
+        return
+    _grouped(x, token_of_row, tile_expert, w_gate_up, pad, inner, act)
 
 
 def moe_down(act: torch.Tensor, tile_expert: torch.Tensor, w_down: torch.Tensor, y: torch.Tensor) -> None:
     """y[r] = w_down[e] act[r] in float32 for the rows of used tiles.  ``w_down`` ``[E, hidden, inner]``."""
     if y.dtype != torch.float32:
         raise KernelError("moe_down: the experts' outputs are float32")
-    _grouped(act, None, tile_expert, w_down, None, y)
+    if _tile_of(y.shape[0], tile_expert) == MOE_TC_TILE_ROWS:
+        _grouped_tc(act, tile_expert, w_down, y, 0)
+        return
+    _grouped(act, None, tile_expert, w_down, None, w_down.shape[1], y)
 
 
 def moe_combine(y: torch.Tensor, row_of_pair: torch.Tensor, weight: torch.Tensor, shared: Optional[torch.Tensor],

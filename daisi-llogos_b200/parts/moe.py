@@ -7,7 +7,8 @@ runs) where the layer has one.
 
 On the device the step's (token, choice) pairs are put in the order of their experts, every expert's run of rows
 filled up to a whole tile (``ops.moe_plan``), so that two grouped products (gate/up with the gating as its epilogue,
-then down) work tile by tile, each tile with one expert's matrices; ``ops.moe_combine`` adds a token's rows with their
+then down) work tile by tile, each tile with one expert's matrices (a prompt step in bfloat16: tiles of 128 rows on the
+grouped tcgen05 product of csrc/gemm_tc.cu; otherwise tiles of 32 rows on the kernels of csrc/moe.cu); ``ops.moe_combine`` adds a token's rows with their
 weights, and the shared expert's partial sums, into one float32 set of partials.  Nothing comes back to the host: the
 same launches serve any routing, so a decode step can be recorded once and replayed.
 """
@@ -15,7 +16,7 @@ from __future__ import annotations
 
 import torch
 
-from ..kernels.linear import linear
+from ..kernels.linear import gated_layout, linear
 from .base import Branch, FeedForward, TensorDecl, as_f32, part_class, register_part
 
 
@@ -49,7 +50,7 @@ class MoeFeedForward(FeedForward):
                 sp["tensor_names"] = dict(p["shared_names"])
             self.shared_rel = str(p.get("shared_prefix", "shared."))
             self.shared = part_class("ffn", "swiglu")(sp, prefix + self.shared_rel, env)
-        self.w_router = self.b_router = self.w_gate = self.w_up = self.w_down = None
+        self.w_router = self.b_router = self.w_gate_up = self.w_down = None
 
     def _expert(self, i: int, what: str) -> str:
         return f"experts.{i}.{what}_proj.weight"
@@ -89,8 +90,9 @@ class MoeFeedForward(FeedForward):
         per = {what: [tensors[self._expert(i, what)] for i in range(self.n_exp)] for what in ("gate", "up", "down")}
         if len({w.dtype for ws in per.values() for w in ws}) != 1:
             raise ValueError(f"{self.prefix}: the experts' matrices are stored with different types")
-        self.w_gate = torch.stack(per["gate"]).contiguous()          # [E, inner, hidden]
-        self.w_up = torch.stack(per["up"]).contiguous()
+        # every expert's gate and up matrices as one matrix in the gated layout (gate rows, filled up to a multiple of
+        # 128, then the up rows): what the gating epilogue of the tensor-core product reads, and the other kernels too
+        self.w_gate_up = torch.stack([gated_layout(g, u) for g, u in zip(per["gate"], per["up"])]).contiguous()
         self.w_down = torch.stack(per["down"]).contiguous()          # [E, hidden, inner]
         if self.shared is not None:
             self.shared.bind({rel[len("shared:"):]: t for rel, t in tensors.items() if rel.startswith("shared:")})
@@ -107,13 +109,20 @@ class MoeFeedForward(FeedForward):
             if self.w_router is None:
                 self.w_router = as_f32(self.w_router_same, self.env)
             ops.moe_route(x, self.w_router, self.b_router, choice, weight)
-        cap = ops.moe_row_capacity(pairs, self.n_exp)
+        tile = ops.moe_tile_rows(x.dtype, pairs, self.n_exp, self.hidden, self.inter)
+        cap = ops.moe_row_capacity(pairs, self.n_exp, tile)
         row_of_pair = ctx.buffer("moe.row_of_pair", (pairs,), torch.int32)
         token_of_row = ctx.buffer("moe.token_of_row", (cap,), torch.int32)
-        tile_expert = ctx.buffer("moe.tile_expert", (cap // ops.MOE_TILE_ROWS,), torch.int32)
+        tile_expert = ctx.buffer("moe.tile_expert", (cap // tile,), torch.int32)
         ops.moe_plan(choice, self.n_exp, row_of_pair, token_of_row, tile_expert)
         act = ctx.buffer("moe.act", (cap, self.inter))
-        ops.moe_gated(x, token_of_row, tile_expert, self.w_gate, self.w_up, act)
+        if tile == ops.MOE_TILE_ROWS:
+            ops.moe_gated(x, token_of_row, tile_expert, self.w_gate_up, act)
+        else:
+            # a prompt step on the tensor cores: the layout's rows as a matrix of their own, then the grouped tcgen05 product
+            rows = ctx.buffer("moe.rows", (cap, self.hidden))
+            ops.moe_gather_rows(x, token_of_row, rows)
+            ops.moe_gated(rows, None, tile_expert, self.w_gate_up, act)
         y = ctx.buffer("moe.y", (cap, self.hidden), torch.float32)
         ops.moe_down(act, tile_expert, self.w_down, y)
         shared = self.shared.forward(x, ctx).data if self.shared is not None else None

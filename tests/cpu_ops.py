@@ -158,9 +158,13 @@ MOE_MAX_EXPERTS = 1024
 MOE_MAX_TOP = 32
 
 
-def moe_row_capacity(pairs, n_experts):
-    cap = pairs + n_experts * (MOE_TILE_ROWS - 1)
-    return -(-cap // MOE_TILE_ROWS) * MOE_TILE_ROWS
+def moe_tile_rows(dtype, pairs, n_experts, hidden, inner):
+    return MOE_TILE_ROWS
+
+
+def moe_row_capacity(pairs, n_experts, tile=MOE_TILE_ROWS):
+    cap = pairs + n_experts * (tile - 1)
+    return -(-cap // tile) * tile
 
 
 def moe_route(x, w_router, b_router, choice, weight):
@@ -194,15 +198,16 @@ def moe_plan(choice, n_experts, row_of_pair, token_of_row, tile_expert):
         # tiles of an expert without rows stay -1 (it has none)
 
 
-def moe_gated(x, token_of_row, tile_expert, w_gate, w_up, act):
+def moe_gated(x, token_of_row, tile_expert, w_gate_up, act):
     act.zero_()
+    inner, pad = act.shape[1], w_gate_up.shape[1] // 2
     for r in range(token_of_row.numel()):
         t = int(token_of_row[r])
         if t < 0:
             continue
         e = int(tile_expert[r // MOE_TILE_ROWS])
-        g = w_gate[e].float() @ x[t].float()
-        u = w_up[e].float() @ x[t].float()
+        g = w_gate_up[e, :inner].float() @ x[t].float()
+        u = w_gate_up[e, pad:pad + inner].float() @ x[t].float()
         act[r] = (g / (1 + torch.exp(-g)) * u).to(act.dtype)
 
 

@@ -294,7 +294,8 @@ def test_latent_preparation_and_per_head_products(llogos, dtype, nh, dim, rdim, 
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
-@pytest.mark.parametrize("n,hidden,n_exp,top,ff", [(1, 40, 3, 3, 10), (9, 72, 5, 2, 24), (300, 96, 16, 4, 40), (50, 100, 70, 1, 8)])
+@pytest.mark.parametrize("n,hidden,n_exp,top,ff", [(1, 40, 3, 3, 10), (9, 72, 5, 2, 24), (300, 96, 16, 4, 40), (50, 100, 70, 1, 8),
+                                                   (700, 192, 6, 2, 136)])
 def test_expert_kernels(llogos, dtype, n, hidden, n_exp, top, ff):
     """Routing against the plain router; the layout's invariants; the grouped products and the weighted sum against the
     plain mixture given the same choices."""
@@ -335,9 +336,31 @@ def test_expert_kernels(llogos, dtype, n, hidden, n_exp, top, ff):
     # the experts' two products and the weighted sum
     act = torch.empty((cap, ff), dtype=dtype, device="cuda")
     stack = lambda what: torch.stack([w[f"m.e{e}.{what}"] for e in range(n_exp)]).to(dtype).cuda()
-    ops.moe_gated(x.cuda(), token_of_row, tile_expert, stack("gate"), stack("up"), act)
+    pad = -(-ff // 128) * 128
+    gate_up = torch.zeros((n_exp, 2 * pad, hidden), dtype=dtype, device="cuda")       # the gated layout, expert by expert
+    gate_up[:, :ff], gate_up[:, pad:pad + ff] = stack("gate"), stack("up")
+    ops.moe_gated(x.cuda(), token_of_row, tile_expert, gate_up, act)
     y = torch.empty((cap, hidden), dtype=torch.float32, device="cuda")
     ops.moe_down(act, tile_expert, stack("down"), y)
+    if dtype == torch.bfloat16 and hidden % 8 == 0 and ff % 8 == 0:
+        # the same through the layout of 128-row tiles: gathered rows, grouped tcgen05 products
+        cap2 = ops.moe_row_capacity(n * top, n_exp, ops.MOE_TC_TILE_ROWS)
+        rop2 = torch.empty((n * top,), dtype=torch.int32, device="cuda")
+        tor2 = torch.empty((cap2,), dtype=torch.int32, device="cuda")
+        te2 = torch.empty((cap2 // ops.MOE_TC_TILE_ROWS,), dtype=torch.int32, device="cuda")
+        ops.moe_plan(choice, n_exp, rop2, tor2, te2)
+        rows2 = torch.empty((cap2, hidden), dtype=dtype, device="cuda")
+        ops.moe_gather_rows(x.cuda(), tor2, rows2)
+        act2 = torch.full((cap2, ff), 7.0, dtype=dtype, device="cuda")
+        ops.moe_gated(rows2, None, te2, gate_up, act2)
+        y2 = torch.full((cap2, hidden), 7.0, dtype=torch.float32, device="cuda")
+        ops.moe_down(act2, te2, stack("down"), y2)
+        assert ops.gemm_tc_status() == 0
+        a1, a2 = act[row_of_pair.long()].float(), act2[rop2.long()].float()
+        assert float((a1 - a2).abs().max()) <= 2e-2 * float(a1.abs().max())
+        y1, y2r = y[row_of_pair.long()], y2[rop2.long()]
+        assert float((y1 - y2r).abs().max()) <= 2e-2 * float(y1.abs().max())
+        y, row_of_pair = y2, rop2                          # the weighted sum below then checks this path against the plain one
     shared = torch.randn((2, n, hidden), generator=g)
     out = torch.empty((n, hidden), dtype=torch.float32, device="cuda")
     ops.moe_combine(y, row_of_pair, weight, shared.cuda(), out)
@@ -365,6 +388,30 @@ def test_whole_prompt_and_first_tokens(engines, models, name, dtype):
         close(lg, ref, dtype, (name, "whole", n))
         eng.close(slot)
     eng.cache.audit()
+
+
+def test_a_long_prompt_takes_the_experts_through_the_grouped_tensor_core_product(engines, models):
+    """900 tokens in one step: enough (token, choice) pairs that the bfloat16 experts run on tiles of 128 rows; the same
+    prompt in portions of 200 (small tiles) and token by token at its end give the same logits within the bound."""
+    from importlib import import_module
+    ops = import_module("daisi-llogos_b200.kernels.ops")
+    name, dtype = "tensor", torch.bfloat16
+    cfg = models[name, dtype][1]
+    ml = cfg["layers"][0]["mlp"]
+    assert ops.moe_tile_rows(dtype, 900 * ml["router"]["top"], ml["router"]["experts"], cfg["width"], ml["expert"]["ff"]) == ops.MOE_TC_TILE_ROWS
+    eng = engines(name, dtype)
+    toks = tokens_for(cfg, 900, 31)
+    ref = plain(models, name, dtype, toks)
+    want = list(range(0, 900, 7)) + [899]
+    slot = eng.open()
+    lg = eng.step([(slot, toks)], [want])
+    close(lg, ref[want], dtype, ("long prompt",))
+    eng.close(slot)
+    assert ops.gemm_tc_status() == 0
+    slot = eng.open()
+    got = [eng.step([(slot, toks[a:a + 200])], [list(range(len(toks[a:a + 200])))]).clone() for a in range(0, 900, 200)]
+    close(torch.cat(got), ref, dtype, ("long prompt in portions",))
+    eng.close(slot)
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
