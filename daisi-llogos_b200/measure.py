@@ -45,6 +45,8 @@ class ModelCosts:
     bytes_per_param: int
     kv_units: Sequence[tuple]   # per cache unit: (bytes per token, window or 0)
     attn_flops_per_pair: int    # flops per (query, key) pair summed over the layers: 4 * heads * head size each
+    active_params: int = -1     # elements of the matrices ONE token passes through (less than matrix_params where a token
+                                # uses a few of many experts); -1: all of them
 
     def decode_step_bytes(self, lengths: Sequence[int], hidden_size: int = 0) -> float:
         """Bytes one decode step must read: every matrix once, the head once, and the keys and values that the
@@ -60,7 +62,8 @@ class ModelCosts:
         element and token, the causal score and value products, and the head on the wanted rows."""
         before = before or [0] * len(counts)
         pairs = sum(c * b + c * (c + 1) / 2 for c, b in zip(counts, before))
-        return 2.0 * sum(counts) * self.matrix_params + 2.0 * wanted_rows * self.head_params + self.attn_flops_per_pair * pairs
+        per_token = self.matrix_params if self.active_params < 0 else self.active_params
+        return 2.0 * sum(counts) * per_token + 2.0 * wanted_rows * self.head_params + self.attn_flops_per_pair * pairs
 
 
 def model_costs(model) -> ModelCosts:
@@ -83,19 +86,25 @@ def model_costs(model) -> ModelCosts:
     head = matrices(model.head)
     if head == 0:                                        # tied: the embedding table serves as the output matrix
         head = int(model.spec.vocab_size) * int(model.spec.hidden_size)
-    matrix = 0
+    matrix = active = 0
     kv, attn = [], 0
     for e in model.spec.schedule:
         block = model.blocks[e.layer]
-        matrix += sum(matrices(part) for part in block.parts.values())
+        for part in block.parts.values():
+            stored = matrices(part)
+            matrix += stored
+            # a part of which a token uses only a share of the matrices says how much (``active_matrix_params``)
+            used = getattr(part, "active_matrix_params", None)
+            active += stored if used is None else int(used())
         need = block.cache_need()
         if isinstance(need, KvNeed) and e.cache_of is None:
-            kv.append((need.num_kv_heads * (need.head_dim + (need.value_dim or need.head_dim)) * elem, need.window))
+            values = 0 if need.values_in_keys else (need.value_dim or need.head_dim)      # values read out of the keys cost no bytes of their own
+            kv.append((need.num_kv_heads * (need.head_dim + values) * elem, need.window))
         for part in block.parts.values():
-            nh, hd = getattr(part, "nh", None), getattr(part, "hd", None)
+            nh, hd = getattr(part, "nh", None), getattr(part, "hd", None) or getattr(part, "kd", None)
             if nh and hd:
                 attn += 2 * nh * (hd + (getattr(part, "vd", None) or hd))
-    return ModelCosts(matrix, head, elem, tuple(kv), attn)
+    return ModelCosts(matrix, head, elem, tuple(kv), attn, active)
 
 
 def decode_bytes_of_run(costs: ModelCosts, prompt_lengths: Sequence[int], generated: Sequence[int]):

@@ -97,6 +97,11 @@ class MoeFeedForward(FeedForward):
         if self.shared is not None:
             self.shared.bind({rel[len("shared:"):]: t for rel, t in tensors.items() if rel.startswith("shared:")})
 
+    def active_matrix_params(self) -> int:
+        """Elements of the matrices one token passes through: the router, ``top`` experts, the shared expert."""
+        shared = 3 * self.hidden * self.shared.inter if self.shared is not None else 0
+        return self.n_exp * self.hidden + self.top * 3 * self.hidden * self.inter + shared
+
     def forward(self, x, ctx) -> Branch:
         ops = ctx.ops
         n = x.shape[0]

@@ -125,3 +125,28 @@ def test_other_norms_refuse_a_branch_of_several_sublayers(llogos):
     norm = llogos.parts.base.part_class("norm", "rmsnorm")({"size": 4, "eps": 1e-5}, "n.", None)
     with pytest.raises(ValueError, match="several sublayers"):
         norm.forward(torch.zeros(2, 4), Branch(torch.zeros(1, 2, 4), scale=0.5), None)
+
+
+def test_cost_model_counts_chosen_experts_and_one_row_per_latent_position(llogos):
+    import importlib
+    measure = importlib.import_module("daisi-llogos_b200.measure")
+    cfg = FM.CONFIGS["mixed"]
+    model = llogos.weights.build_model(cfg, dtype=torch.bfloat16, device="cpu", ops=cpu_ops)
+    costs = measure.model_costs(model)
+    d = cfg["width"]
+    stored = active = 0
+    for lay in cfg["layers"]:
+        m = lay["mixer"]
+        if lay["type"] == "attention":
+            n = d * (m["heads"] * m["dim"] + m["kv_heads"] * (m["dim"] + m["vdim"])) + d * m["heads"] * m["vdim"]
+        else:
+            n = d * (m["heads"] * (m["dim"] + m["rot_dim"]) + m["kv_rank"] + m["rot_dim"]) + m["kv_rank"] * m["heads"] * (m["dim"] + m["vdim"]) \
+                + d * m["heads"] * m["vdim"]
+        stored, active = stored + n, active + n
+        ml = lay["mlp"]
+        if ml:
+            e_n, top, ff, sh = ml["router"]["experts"], ml["router"]["top"], ml["expert"]["ff"], (ml.get("shared") or {}).get("ff", 0)
+            stored += e_n * d + e_n * 3 * d * ff + 3 * d * sh
+            active += e_n * d + top * 3 * d * ff + 3 * d * sh
+    assert costs.matrix_params == stored and costs.active_params == active
+    assert costs.kv_units[0] == (2 * (16 + 24) * 2, 37) and costs.kv_units[1] == ((24 + 8) * 2, 50)
