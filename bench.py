@@ -411,7 +411,7 @@ def design_configs(size, design="karitar"):
 
 _TIMED_OPS = ("embed_rows", "add_rmsnorm", "hc_add_rmsnorm", "qk_prep", "qkv_row_prep", "gemm_tc", "gemm_tc_act", "gemm_tc_qkv",
               "act_rows", "silu_mul", "attn_prefill", "attn_decode", "kv_write", "add_layernorm", "latent_prep", "head_linear",
-              "moe_route", "moe_plan", "moe_gated", "moe_down", "moe_combine")
+              "moe_route", "moe_topk", "moe_plan", "moe_gather_rows", "moe_gated", "moe_down", "moe_combine")
 
 
 def _kernel_label(name, args, kw):
@@ -454,9 +454,10 @@ def _kernel_cost(name, args, kw, keys_read):
     if name in ("moe_gated", "moe_down"):
         # the pairs' rows (the layout's filling rows left out) against the matrices of the experts they can reach
         w = args[3] if name == "moe_gated" else args[2]
-        rows_out = args[5] if name == "moe_gated" else args[3]
-        n_exp, n_out, n_in = w.shape
-        pairs = max(1, rows_out.shape[0] - n_exp * (ops_tile() - 1))
+        rows_out = args[4] if name == "moe_gated" else args[3]
+        tiles = args[2] if name == "moe_gated" else args[1]
+        n_exp, n_in, n_out = w.shape[0], w.shape[2], rows_out.shape[1]
+        pairs = max(1, rows_out.shape[0] - n_exp * (rows_out.shape[0] // tiles.numel() - 1))
         mats = 2 if name == "moe_gated" else 1
         moved = min(n_exp, pairs) * mats * n_out * n_in * w.element_size() + pairs * (n_in * args[0].element_size() + n_out * rows_out.element_size())
         return moved, 2.0 * mats * pairs * n_out * n_in
@@ -468,11 +469,6 @@ def _kernel_cost(name, args, kw, keys_read):
         moved = sum(t.nbytes for t in tensors if t.dim() != 4)
         return moved, 0.0
     return sum(t.nbytes for t in tensors), 0.0
-
-
-def ops_tile():
-    from importlib import import_module
-    return import_module("daisi-llogos_b200.kernels.ops").MOE_TILE_ROWS
 
 
 def probe_designs(torch, L, ops, pk, sizes, batch, which="karitar"):
