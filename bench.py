@@ -378,13 +378,13 @@ def fipavik_config(size):
     width, heads, kv, hd, ff, window, _ = DESIGN_SIZES[size]
     mask = {"size": window or 2048}
     att = {"heads": heads, "kv_heads": kv, "dim": hd, "vdim": hd, "scale": hd ** -0.5, "mask": mask,
-           "rot": {"base": 500000.0, "dims": hd // 2}, "v_mix": True}
+           "rot": {"base": 1000000.0, "dims": hd // 2}, "v_mix": True}
     lat = {"heads": heads, "dim": hd, "rot_dim": hd // 4, "vdim": hd, "kv_rank": 3 * hd // 4, "scale": (hd + hd // 4) ** -0.5,
-           "mask": mask, "rot": {"base": 20000.0, "dims": hd // 4}}
+           "mask": mask, "rot": {"base": 10000.0, "dims": hd // 4}}
     mlp = {"kind": "moe", "router": {"experts": FIPAVIK_EXPERTS, "top": FIPAVIK_TOP}, "expert": {"ff": ff // 8}, "shared": {"ff": ff // 2}}
     layers = [{"type": "latent_attention" if i % 2 == 0 else "attention", "mixer": dict(lat if i % 2 == 0 else att), "mlp": dict(mlp)}
               for i in range(DESIGN_LAYERS)]
-    return {"architecture": "Fipavik", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+    return {"architecture": "Fipavik", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.7,
             "layers": layers}
 
 

@@ -56,7 +56,7 @@ CONFIGS = {
         layer(attention(4, 2, 64, 64, 70, 32, v_mix=True), moe(6, 3, 48, 0)),
         layer(attention(6, 2, 48, 48, 100, 48), moe(4, 2, 64, 32)),
         layer(attention(2, 2, 64, 64, 128, 64, v_mix=True), None),
-    ], vocab=300, width=128, mult=0.5),
+    ], vocab=300, width=128, mult=0.8),
     # sizes that fit no vector access and no tensor-core tile; a window and a chunk of one position (a query sees
     # itself alone); every expert chosen (top = experts); a residual factor of one
     "odd": config([
