@@ -172,5 +172,20 @@ def load_library(name: str) -> ctypes.CDLL:
         return lib
 
 
+def prefetch(names) -> None:
+    """Starts compiling the libraries ``names`` that are not built yet, each in a thread of its own, and returns at
+    once: in a fresh checkout the long compilations then run side by side instead of one after another as the first
+    step meets them (``load_library`` waits for a compilation under way through the library's lock file).  A failure
+    here is not reported; whoever needs the library gets the error from ``load_library``."""
+    def work(name):
+        try:
+            compile_library(name)
+        except Exception:
+            pass
+    for name in names:
+        if name in SOURCES and not os.path.isfile(library_path(name)):
+            threading.Thread(target=work, args=(name,), daemon=True).start()
+
+
 def build_all(verbose: bool = True) -> List[str]:
     return [compile_library(n, verbose=verbose) for n in SOURCES]

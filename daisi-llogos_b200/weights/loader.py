@@ -89,9 +89,16 @@ def load_model(model_dir: str, *, dtype: torch.dtype = torch.bfloat16, device="c
     device = torch.device(device)
     if dtype not in (torch.bfloat16, torch.float32):
         raise ValueError(f"compute type must be bfloat16 or float32, got {dtype}")
+    config_dict = read_config_json(model_dir)
+    if device.type == "cuda" and ops is None:
+        # What every model needs at its first step, compiled side by side from the start in a fresh checkout: the
+        # embedding's library, and the matrix products' (tensor cores take bfloat16 rows of a multiple of 8 elements).
+        from ..csrc.build import prefetch
+        arch = architecture_of(config_dict)
+        width = arch.build_spec(arch.read_config(config_dict)).hidden_size
+        prefetch(["elementwise", "gemm_tc" if dtype == torch.bfloat16 and width % 8 == 0 else "gemm_simt"])
     if ops is None:
         ops = _ops_for(device)
-    config_dict = read_config_json(model_dir)
     model = build_model(config_dict, dtype=dtype, device=device, ops=ops)
     decls = model.tensor_decls()
     files = ModelFiles(model_dir)
