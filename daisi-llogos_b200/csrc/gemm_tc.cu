@@ -241,8 +241,6 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
     }
   };
   const bool grouped = SWAP == 1 && MT == 1 && p.tile_group != nullptr;
-  // the group of a tile's tokens (read only after the dependency wait)
-  auto group_of = [&](int tile) { return p.tile_group[tile % m_tiles]; };
   // first operand: MT tiles of 128 rows
   auto load_first = [&](unsigned char* dst, int kb, int o0, uint64_t* bar) {
 #pragma unroll
@@ -250,8 +248,30 @@ __global__ void __launch_bounds__(GEMM_THREADS) gemm_tc_kernel(const __grid_cons
   };
   // A block works through tiles blockIdx.x, blockIdx.x + gridDim.x, ...: token tiles of one weight tile are neighbours
   // in that order, so blocks running side by side share the weight tile in L2.
-  auto first_offset = [&](int tile) { return (SWAP ? tile % m_tiles : tile / n_tiles_n) * (GATED_ROWS ? p.gate_rows : BM * MT); };
-  auto second_offset = [&](int tile) { return (SWAP ? tile / m_tiles : tile % n_tiles_n) * TN; };
+  // Grouped products take their tiles in another order: GROUP_M token tiles at a time (neighbours in the layout, so mostly
+  // one group's), all feature tiles of those before the next ones.  The blocks that run side by side then work on a few
+  // groups' matrices and a few token tiles, which stay in L2 together: every matrix and every token row is fetched from
+  // memory about once, instead of every token row once per feature tile.
+  constexpr int GROUP_M = 4;
+  const bool by_groups = SWAP == 1 && MT == 1 && p.tile_group != nullptr;
+  auto tile_m = [&](int tile) {           // index of the tile's first-operand tile
+    if (by_groups) {
+      const int g = tile / (GROUP_M * n_tiles_n), rem = tile % (GROUP_M * n_tiles_n);
+      return g * GROUP_M + rem % min(GROUP_M, m_tiles - g * GROUP_M);
+    }
+    return SWAP ? tile % m_tiles : tile / n_tiles_n;
+  };
+  auto tile_n = [&](int tile) {           // index of its second-operand tile
+    if (by_groups) {
+      const int g = tile / (GROUP_M * n_tiles_n), rem = tile % (GROUP_M * n_tiles_n);
+      return rem / min(GROUP_M, m_tiles - g * GROUP_M);
+    }
+    return SWAP ? tile / m_tiles : tile % n_tiles_n;
+  };
+  auto first_offset = [&](int tile) { return tile_m(tile) * (GATED_ROWS ? p.gate_rows : BM * MT); };
+  auto second_offset = [&](int tile) { return tile_n(tile) * TN; };
+  // the group of a tile's tokens (read only after the dependency wait)
+  auto group_of = [&](int tile) { return p.tile_group[tile_m(tile)]; };
   const int nkb_total = (p.k + BK - 1) / BK;
   const int kb0 = split * p.kb_per_split;
   const int nkb = min(p.kb_per_split, nkb_total - kb0);   // >= 1 by construction of the grid
