@@ -423,11 +423,9 @@ def test_residual_after_every_layer(llogos, models, dtype):
     toks = tokens_for(cfg, 50, 4)
     trace = []
     FP.forward(w, cfg, toks, trace=trace)
-    import json, os
+    import os
     for depth in (1, 2, 4, len(cfg["layers"])):
         cut = dict(cfg, layers=cfg["layers"][:depth])
-        if not any(l["mixer"].get("v_mix") for l in cut["layers"]):
-            pass
         keep = {k: v for k, v in w.items() if not (k.startswith("l") and int(k[1:k.index(".")]) >= depth)}
         sub = os.path.join(d, f"cut{depth}")
         FM.write_model(llogos, sub, cut, 0, weights={k: v.to(torch.bfloat16) for k, v in keep.items()})
@@ -503,6 +501,60 @@ def test_unequal_batches_with_slots_and_pages_used_again(engines, models, name, 
             live = [i for i in live if cut[i] < len(seqs[i])]
         eng.cache.audit()
     assert eng.cache.slots.free_count == eng.cache.slots.n_slots
+
+
+def _random_config(seed):
+    """A configuration drawn from the seed: two to five layers of either kind in any order, sizes, masks, rotations, expert
+    counts and the residual factor all drawn; layers that blend values agree in their values' shape, as they must."""
+    g = torch.Generator().manual_seed(1000 + seed)
+    pick = lambda xs: xs[int(torch.randint(0, len(xs), (1,), generator=g))]
+    width = pick([40, 64, 72, 96, 136])
+    kv_blend, vdim_blend = pick([1, 2, 3]), pick([8, 16, 24, 40])
+    layers = []
+    for _ in range(pick([2, 3, 4, 5])):
+        mlp = None if pick([0, 0, 0, 1]) else FM.moe(pick([2, 3, 5, 9]), 1, pick([8, 24, 40]), pick([0, 16, 56]))
+        if mlp:
+            mlp["router"]["top"] = pick(list(range(1, mlp["router"]["experts"] + 1)))
+        if pick([0, 1]):
+            dim = pick([8, 16, 24, 32, 64])
+            blend = bool(pick([0, 1]))
+            kv = kv_blend if blend else pick([1, 2, 4])
+            mix = FM.attention(kv * pick([1, 2, 3]), kv, dim, vdim_blend if blend else pick([8, dim, 48]), pick([1, 3, 17, 64, 65, 150]),
+                               pick([d for d in (2, 4, 8, 16, 32, 64) if d <= dim]), base=pick([50.0, 10000.0, 3e6]), v_mix=blend,
+                               scale=pick([0.05, 0.2, 0.5]))
+        else:
+            rot = pick([2, 4, 8, 16, 32])
+            mix = FM.latent(pick([1, 2, 3, 5, 8]), pick([8, 16, 40]), rot, pick([8, 24, 32]), pick([8, 16, 30, 64, 112]),
+                            pick([1, 2, 31, 64, 100, 160]), base=pick([50.0, 10000.0, 3e6]), scale=pick([0.05, 0.2, 0.5]))
+        layers.append(FM.layer(mix, mlp))
+    return FM.config(layers, vocab=pick([61, 128, 257]), width=width, mult=pick([0.25, 0.6, 1.0, 1.3]), eps=pick([1e-6, 1e-5, 1e-3]))
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_configurations_drawn_at_random(llogos, tmp_path, seed):
+    """float32: a prompt whole, a batch of two unequal prompts decoded together for a dozen steps, against the plain model."""
+    cfg = _random_config(seed)
+    d = str(tmp_path / "m")
+    w = {k: v.float() for k, v in FM.write_model(llogos, d, cfg, seed=seed).items()}
+    model = llogos.weights.load_model(d, dtype=torch.float32, device="cuda:0")
+    eng = llogos.engine.Engine(model, max_tokens=64 * 12)
+    seqs = [tokens_for(cfg, n, seed * 7 + n) for n in (171, 40)]
+    refs = [FP.forward(w, cfg, s) for s in seqs]
+    slot = eng.open()
+    close(eng.step([(slot, seqs[0])], [list(range(len(seqs[0])))]), refs[0], torch.float32, ("random", seed, "whole"))
+    eng.close(slot)
+    slots = [eng.open(), eng.open()]
+    cut = [len(s) - 12 for s in seqs]
+    lg = eng.step([(sl, s[:c]) for sl, s, c in zip(slots, seqs, cut)])
+    for i in range(2):
+        close(lg[i], refs[i][cut[i] - 1], torch.float32, ("random", seed, "prompt", i))
+    for k in range(12):
+        lg = eng.step([(sl, [s[c + k]]) for sl, s, c in zip(slots, seqs, cut)])
+        for i in range(2):
+            close(lg[i], refs[i][cut[i] + k], torch.float32, ("random", seed, "decode", i, k))
+    for sl in slots:
+        eng.close(sl)
+    eng.cache.audit()
 
 
 @pytest.mark.parametrize("dtype", DTYPES, ids=IDS)
